@@ -1,0 +1,331 @@
+#!/usr/bin/env python
+"""Benchmark of the NVFP4 block-scaled matmul hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c1|c2|c3|c4]
+
+A step is one pass of the hot path over one batch of seeded synthetic input (the leaderboard
+harness that generated the reference's inputs is not part of the reference; see
+nvfp4_gemm_b200/inputs.py).  At N = 1 the workload is the decode-shaped GEMM the reference's
+numbers are quoted on (M=128, N=7168, K=16384, L=1).  At N > 1 the workload is the only one the
+path partitions: M=8192, N=28672, K=8192 split column-parallel over N, with the fp16 column
+blocks all-gathered (strong scaling: total work fixed).
+
+Rank 0 prints ONE JSON line.  `value` is device-timed throughput with inputs resident in HBM;
+`e2e` times the public `custom_kernel` call with host buffers, copies included.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    "c1": dict(m=128, n=7168, k=16384, l=1, bound="hbm", name="C1 decode GEMM m128 n7168 k16384 l1"),
+    "c2": dict(m=7168, n=1, k=16384, l=4, bound="hbm", name="C2 GEMV m7168 k16384 l4"),
+    "c3": dict(m=4096, n=7168, k=7168, l=1, bound="tensor", name="C3 prefill GEMM m4096 n7168 k7168 l1"),
+    "c4": dict(m=8192, n=28672, k=8192, l=1, bound="tensor", name="C4 GEMM m8192 n28672 k8192 l1 (column-parallel over N)"),
+}
+FP4_DENSE_PEAK_TFLOPS = 9000.0   # nominal dense FP4 tensor peak of one B200 (no measured FP4 figure exists)
+
+
+def algorithmic_flops(w):
+    return 2.0 * w["m"] * w["n"] * w["k"] * w["l"]
+
+
+def algorithmic_bytes(w):
+    m, n, k, l = w["m"], w["n"], w["k"], w["l"]
+    return l * (m * k / 2 + n * k / 2 + m * k / 16 + n * k / 16 + 2 * m * n)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return dict(hbm_gbs=float(d["hbm_gbs"]), source="measured")
+    return dict(hbm_gbs=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-i", str(self.index), "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                mx = float(s[1])
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return dict(sm_mhz=(sm[len(sm) // 2] if sm else None), sm_max_mhz=mx, reasons=sorted(reasons), samples=len(sm))
+
+
+def cpu_baseline_sample(w, threads=0, budget_s=12.0):
+    """Times the CPU oracle (C restatement; the reference has no CPU code for this path) on a
+    bounded slice of the workload: all of A against the first `cols` rows of B."""
+    import numpy as np
+    from nvfp4_gemm_b200.inputs import generate_input
+    from oracle import nvfp4_oracle as O
+    O.build_c()
+    cores = threads or O.c_max_threads()
+    m, k = min(w["m"], 128), w["k"]
+    n_full = w["n"]
+    # ~0.2 GFLOP/s/core lower bound is far too pessimistic; start small and grow to the budget
+    cols = min(n_full, 256) if n_full > 1 else 1
+    rows = m if n_full > 1 else min(w["m"], 2048)
+    data = generate_input(rows, cols, k, 1, 1111, device="cpu")
+    a, b, sfa, sfb = O.tensors_to_numpy(data)
+    t0 = time.perf_counter()
+    O.ref_gemm_c(a, b, sfa, sfb, threads=cores)
+    dt = time.perf_counter() - t0
+    reps = int(max(1, min(20, budget_s / max(dt, 1e-3))))
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        O.ref_gemm_c(a, b, sfa, sfb, threads=cores)
+    dt = (time.perf_counter() - t0) / reps
+    flops = 2.0 * rows * cols * k
+    return dict(tflops=flops / dt / 1e12, seconds=dt, cores=cores,
+                sample=f"{rows}x{cols}x{k} slice of the workload (all K, first {cols} of {n_full} B rows), {reps} repeats")
+
+
+def run_reference_arm(args, w):
+    """The 'reference' arm: the path's CPU implementation on the host cores.  The reference has no
+    CPU code (and its harness ref_kernel is absent), so this is the oracle port."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals = []
+    for _ in range(args.warmup):
+        cpu_baseline_sample(w, budget_s=0.5)
+    info = None
+    t_all = time.perf_counter()
+    for _ in range(args.steps):
+        info = cpu_baseline_sample(w, budget_s=2.0)
+        vals.append(info["tflops"])
+    value = sum(vals) / len(vals)
+    line = dict(impl="reference", metric="nvfp4_matmul_throughput", value=value, unit="TFLOP/s", n_gpus=args.gpus,
+                steps=args.steps, warmup=args.warmup, ms_per_step=1e3 * (time.perf_counter() - t_all) / args.steps,
+                higher_is_better=True, scaling="strong" if args.gpus > 1 else "weak", vs_baseline=None, dtype="e2m1 x ue4m3 -> f32 -> f16",
+                data="synthetic", config=dict(workload=w["name"]),
+                cpu_baseline=dict(value=value, unit="TFLOP/s", cores=info["cores"], kind="port", sample=info["sample"]),
+                e2e=dict(value=value, unit="TFLOP/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the secondary per-config table")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    wl_key = args.workload or ("c1" if args.gpus == 1 else "c4")
+    w = WORKLOADS[wl_key]
+    if args.impl == "reference":
+        run_reference_arm(args, w)
+        return
+
+    import torch
+    from nvfp4_gemm_b200 import submission as S
+    from nvfp4_gemm_b200.inputs import generate_input
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    if world > 1:
+        from nvfp4_gemm_b200.multi_gpu import bench_column_parallel
+        bench_column_parallel(args, w, rank, world, dev, ClockSampler, measured_peaks, algorithmic_flops)
+        return
+
+    peaks = measured_peaks()
+    l2_bytes = torch.cuda.get_device_properties(dev).L2_cache_size
+    set_bytes = algorithmic_bytes(w)
+    n_sets = int(min(8, max(3, -(-3 * l2_bytes // int(set_bytes)))))   # rotate over > 3x L2 of inputs
+    sets = [generate_input(w["m"], w["n"], w["k"], w["l"], 1111 + i, device=dev) for i in range(n_sets)]
+
+    def step(i):
+        return S.custom_kernel(sets[i % n_sets])
+
+    for i in range(args.warmup):
+        step(i)
+    S.check_status()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = S.launch_count()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    torch.cuda.synchronize()
+    ev[0].record()
+    for i in range(args.steps):
+        step(i)
+        ev[i + 1].record()
+    torch.cuda.synchronize()
+    total_ms = ev[0].elapsed_time(ev[-1])
+    per_launch_ms = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps))
+    launches = S.launch_count() - launches0
+    S.check_status()
+    kernel_name = S.last_kernel()
+
+    ms_per_step = total_ms / args.steps
+    flops = algorithmic_flops(w)
+    byts = algorithmic_bytes(w)
+    tflops = flops / (ms_per_step * 1e-3) / 1e12
+    gbs = byts / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end through custom_kernel with host buffers (pinned), copies inside the timed region
+    def _raw(t):
+        # the tensors are dense permutations of contiguous storage: view them as flat memory
+        return torch.as_strided(t.view(torch.uint8) if t.element_size() == 1 else t, (t.numel(),), (1,))
+
+    host_sets = [[_raw(t).cpu().pin_memory() for t in s[:6]] for s in sets[:2]]
+    dev_buf = [torch.empty_like(t) for t in sets[0]]
+    c_host = torch.empty(sets[0][6].numel(), dtype=torch.float16).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in host_sets[0])
+    d2h = c_host.numel() * c_host.element_size()
+
+    def e2e_step(i):
+        hs = host_sets[i % len(host_sets)]
+        for j in range(6):
+            _raw(dev_buf[j]).copy_(hs[j], non_blocking=True)
+        S.custom_kernel(tuple(dev_buf))
+        c_host.copy_(_raw(dev_buf[6]), non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 20))
+    for i in range(3):
+        e2e_step(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    clocks = sampler.stop()
+
+    if w["bound"] == "hbm":
+        roofline = dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s", frac=gbs / peaks["hbm_gbs"],
+                        traffic=None, peak_source=peaks["source"], kernel=kernel_name)
+    else:
+        roofline = dict(bound="tensor", achieved=tflops, peak=FP4_DENSE_PEAK_TFLOPS, unit="TFLOP/s",
+                        frac=tflops / FP4_DENSE_PEAK_TFLOPS, traffic=None, peak_source="nominal dense FP4", kernel=kernel_name)
+    traffic_path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    if os.path.exists(traffic_path):
+        with open(traffic_path) as f:
+            roofline["traffic"] = json.load(f).get(wl_key)
+
+    line = dict(metric="nvfp4_matmul_throughput", value=tflops, unit="TFLOP/s", n_gpus=1, steps=args.steps,
+                warmup=args.warmup, ms_per_step=ms_per_step, higher_is_better=True, scaling="weak", vs_baseline=None,
+                dtype="e2m1 x ue4m3 -> f32 -> f16", data="synthetic",
+                config=dict(workload=w["name"], timing=f"CUDA events; {n_sets} rotating input sets = {n_sets * set_bytes / 1e6:.0f} MB > L2 {l2_bytes / 1e6:.0f} MB",
+                            us_per_step=ms_per_step * 1e3, us_median_launch=per_launch_ms[len(per_launch_ms) // 2] * 1e3,
+                            us_min_launch=per_launch_ms[0] * 1e3, gb_per_s=gbs,
+                            reference_published_us={"cuBLASLt": 22.6, "cute_dsl_template": 144.0, "hand_written_tcgen05": 459.0} if wl_key == "c1" else None),
+                roofline=roofline,
+                e2e=dict(value=flops / (e2e_ms * 1e-3) / 1e12, unit="TFLOP/s", ms_per_step=e2e_ms, h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
+                gpu_launches=int(launches), clocks=clocks)
+
+    if not args.no_extra:
+        line["other_configs"] = extra_table(S, generate_input, dev, peaks)
+    if not args.no_cpu_baseline:
+        cb = cpu_baseline_sample(w)
+        line["cpu_baseline"] = dict(value=cb["tflops"], unit="TFLOP/s", cores=cb["cores"], kind="port", sample=cb["sample"])
+    print(json.dumps(line), flush=True)
+
+
+def extra_table(S, generate_input, dev, peaks):
+    """Device-timed µs / TFLOPS / GB/s for the other single-GPU configurations and the same-GPU
+    cuBLASLt comparator (torch._scaled_mm), reported beside the headline line."""
+    import torch
+    out = {}
+
+    def time_fn(fn, n_sets, iters=30):
+        for i in range(min(3, iters)):
+            fn(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(iters):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters * 1e3
+
+    def flat(t):
+        return torch.as_strided(t.view(torch.uint8), (t.numel(),), (1,)).view(t.dtype)
+
+    for key in ("c1", "c2", "c3"):
+        w = WORKLOADS[key]
+        n_sets = 4 if key == "c1" else 3
+        sets = [generate_input(w["m"], w["n"], w["k"], w["l"], 2000 + i, device=dev) for i in range(n_sets)]
+        us = time_fn(lambda i: S.custom_kernel(sets[i % n_sets]), n_sets)
+        rec = dict(us=us, tflops=algorithmic_flops(w) / us / 1e6, gb_per_s=algorithmic_bytes(w) / us / 1e3, kernel=S.last_kernel())
+        rec["frac_hbm_measured"] = rec["gb_per_s"] / peaks["hbm_gbs"]
+        rec["frac_fp4_nominal"] = rec["tflops"] / FP4_DENSE_PEAK_TFLOPS
+        if w["n"] > 1:
+            try:
+                ar = [(s[0][:, :, 0], s[1][:, :, 0].t(), flat(s[4]), flat(s[5])) for s in sets]
+                cus = time_fn(lambda i: torch._scaled_mm(*ar[i % n_sets], out_dtype=torch.float16), n_sets)
+                rec["cublaslt_us"] = cus
+                rec["cublaslt_tflops"] = algorithmic_flops(w) / cus / 1e6
+            except Exception as e:  # noqa: BLE001
+                rec["cublaslt_us"] = None
+                rec["cublaslt_error"] = str(e)[:200]
+        out[key] = rec
+        del sets
+        torch.cuda.empty_cache()
+    S.check_status()
+    return out
+
+
+if __name__ == "__main__":
+    main()

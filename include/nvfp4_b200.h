@@ -1,0 +1,129 @@
+/*
+ * nvfp4_b200 -- C ABI of the B200 (sm_100a) NVFP4 block-scaled matmul library.
+ *
+ * Every entry point takes raw device pointers, sizes and strides; there are no C++ or
+ * torch types in the interface.  All functions return 0 on success and a negative
+ * NVFP4_ERR_* code on failure; nvfp4_last_error() gives the message for the calling thread.
+ * Work is enqueued on the CUDA stream passed in (a cudaStream_t cast to void*; NULL is the
+ * legacy default stream, which is what the reference launches on, s_128t.py:579-582) and is
+ * asynchronous with respect to the host.
+ *
+ * File paths in the comments below are paths inside the reference project.
+ */
+#ifndef NVFP4_B200_H
+#define NVFP4_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NVFP4_OK 0
+#define NVFP4_ERR_INVALID_ARGUMENT (-1) /* bad shape, alignment, stride or null pointer */
+#define NVFP4_ERR_CUDA (-2)             /* a CUDA runtime / driver call failed */
+#define NVFP4_ERR_DEVICE_TIMEOUT (-3)   /* a bounded wait inside a kernel ran out */
+#define NVFP4_ERR_UNSUPPORTED (-4)      /* not an sm_100 device, or feature not built */
+
+/*
+ * One block-scaled matmul problem:  C[m,n,l] = sum_k A[m,k,l]*SFA[m,k/16,l] * B[n,k,l]*SFB[n,k/16,l].
+ * This is the 7-tuple of the reference operator (template.py:9-18) spelled as pointers:
+ *   a, b           packed e2m1, two values per byte (low nibble = lower k), K contiguous
+ *   sfa, sfb       e4m3 (bias 7) scale per 16 K elements, plain [rows, K/16] layout
+ *   sfa_perm, ...  the same scales in 512-byte atoms of 128 rows x 4 scales
+ *                  ([32,4,rest_rows,4,rest_k,L], ref.txt:31, s_128t.py:554-562)
+ *   c              fp16 output
+ * The GEMM reads only the permuted scales (like s_128t.py:542-584 and sub_cub.py:82-88); the
+ * GEMV reads only the plain ones (like old_files/1.py:697-698).  Unused pointers may be NULL.
+ * Strides of a, b, sf* are in bytes, strides of c in fp16 elements.
+ */
+typedef struct nvfp4_problem {
+    const void* a;
+    const void* b;
+    const void* sfa;
+    const void* sfb;
+    const void* sfa_perm;
+    const void* sfb_perm;
+    void* c;
+    int32_t m, n, k, l;
+    int64_t a_row_stride, a_batch_stride;
+    int64_t b_row_stride, b_batch_stride;
+    int64_t sfa_row_stride, sfa_batch_stride;
+    int64_t sfb_row_stride, sfb_batch_stride;
+    int64_t sfa_perm_batch_stride, sfb_perm_batch_stride;
+    int64_t c_row_stride, c_batch_stride;
+} nvfp4_problem;
+
+/* Kernel selection override for tests and tuning; zero in every field = automatic. */
+typedef struct nvfp4_gemm_config {
+    int32_t tile_n;    /* 0 auto, 128 or 256 */
+    int32_t epilogue;  /* 0 auto, 1 = 16-byte global stores, 2 = TMA store */
+    int32_t grid;      /* 0 auto (one CTA per SM), else number of persistent CTAs */
+    int32_t cta_group; /* 0 auto, 1 = one CTA per tile, 2 = CTA pair per 256-row tile */
+} nvfp4_gemm_config;
+
+/*
+ * Tensor-core GEMM (tcgen05.mma kind::mxf4nvf4.block_scale).  Replaces
+ * cuda_nvfp4_gemm_tcgen05(A, B, SFA, SFB, SFA_perm, SFB_perm, C) of s_128t.py:542-584.
+ * Requires n % 128 == 0, k % 256 == 0 (task.yml:24), 16-byte aligned pointers and row strides.
+ * Any m >= 1 is accepted (rows past m are not written).  cfg may be NULL.
+ */
+int nvfp4_gemm(const nvfp4_problem* problem, const nvfp4_gemm_config* cfg, void* stream);
+
+/*
+ * CUDA-core GEMV for n == 1.  Replaces cuda_nvfp4_gemv(A, B, C, SFA, SFB) of
+ * old_files/1.py:610-673.  Requires k % 64 == 0 (task_gemv.yml:24) and 32-byte aligned rows.
+ */
+int nvfp4_gemv(const nvfp4_problem* problem, void* stream);
+
+/*
+ * What custom_kernel(data) calls (template.py:4-25): n == 1 goes to the GEMV, everything
+ * else to the GEMM.
+ */
+int nvfp4_matmul(const nvfp4_problem* problem, void* stream);
+
+/*
+ * Waits for `stream` and returns NVFP4_ERR_DEVICE_TIMEOUT if any kernel launched by this
+ * library on the current device reported a timed-out wait since the last check, else NVFP4_OK.
+ * The reference has no counterpart (its waits are unbounded spins, s_128t.py:124-183,309-319).
+ */
+int nvfp4_check_status(void* stream);
+
+/* Limit, in nanoseconds, of every in-kernel wait (default 1e9).  Returns the previous value. */
+uint64_t nvfp4_set_wait_timeout_ns(uint64_t ns);
+
+/*
+ * Launches a one-CTA kernel that waits on an mbarrier nothing ever arrives at, with the
+ * current wait limit, and synchronises.  Returns NVFP4_ERR_DEVICE_TIMEOUT when the wait gave
+ * up as designed (the context stays usable).  Exists so that the failure path can be tested
+ * without faulting or hanging a GPU.
+ */
+int nvfp4_selftest_bounded_wait(void* stream);
+
+/*
+ * Host-side view of the GEMM's work partition (no GPU needed): the half-open range of
+ * (tile, k-tile) work units that persistent CTA `cta` of `grid` processes, and the scratch
+ * slot used by the first tile it touches if that tile is shared with other CTAs.
+ */
+int nvfp4_plan_units(int total_units, int grid, int cta, int* begin, int* end, int* first_tile_slot, int k_tiles);
+
+/* Bytes of device scratch the library holds on the current device (0 before the first GEMM). */
+size_t nvfp4_scratch_bytes(void);
+
+/* Number of kernels this library has launched in this process (all devices). */
+uint64_t nvfp4_launch_count(void);
+
+/* Name of the kernel variant the last nvfp4_gemm / nvfp4_gemv call on this thread launched. */
+const char* nvfp4_last_kernel(void);
+
+/* Frees cached tensor maps and scratch memory on every device. */
+void nvfp4_shutdown(void);
+
+const char* nvfp4_last_error(void);
+const char* nvfp4_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NVFP4_B200_H */

@@ -1,0 +1,97 @@
+"""ctypes binding of ``libnvfp4_b200.so`` (the C ABI in ``include/nvfp4_b200.h``).
+
+There is no fallback: if the library is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_int, c_int32, c_int64, c_size_t, c_uint64, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libnvfp4_b200.so"
+
+NVFP4_OK = 0
+NVFP4_ERR_INVALID_ARGUMENT = -1
+NVFP4_ERR_CUDA = -2
+NVFP4_ERR_DEVICE_TIMEOUT = -3
+NVFP4_ERR_UNSUPPORTED = -4
+
+EXPORTED_SYMBOLS = (
+    "nvfp4_gemm", "nvfp4_gemv", "nvfp4_matmul", "nvfp4_check_status", "nvfp4_set_wait_timeout_ns",
+    "nvfp4_selftest_bounded_wait", "nvfp4_scratch_bytes", "nvfp4_launch_count", "nvfp4_last_kernel",
+    "nvfp4_shutdown", "nvfp4_last_error", "nvfp4_version", "nvfp4_plan_units",
+)
+
+
+class Nvfp4Error(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"nvfp4_b200 error {code}: {message}")
+        self.code = code
+
+
+class Problem(ctypes.Structure):
+    """Mirror of ``struct nvfp4_problem``."""
+    _fields_ = [
+        ("a", c_void_p), ("b", c_void_p), ("sfa", c_void_p), ("sfb", c_void_p),
+        ("sfa_perm", c_void_p), ("sfb_perm", c_void_p), ("c", c_void_p),
+        ("m", c_int32), ("n", c_int32), ("k", c_int32), ("l", c_int32),
+        ("a_row_stride", c_int64), ("a_batch_stride", c_int64),
+        ("b_row_stride", c_int64), ("b_batch_stride", c_int64),
+        ("sfa_row_stride", c_int64), ("sfa_batch_stride", c_int64),
+        ("sfb_row_stride", c_int64), ("sfb_batch_stride", c_int64),
+        ("sfa_perm_batch_stride", c_int64), ("sfb_perm_batch_stride", c_int64),
+        ("c_row_stride", c_int64), ("c_batch_stride", c_int64),
+    ]
+
+
+class GemmConfig(ctypes.Structure):
+    """Mirror of ``struct nvfp4_gemm_config``."""
+    _fields_ = [("tile_n", c_int32), ("epilogue", c_int32), ("grid", c_int32), ("cta_group", c_int32)]
+
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m nvfp4_gemm_b200.build` "
+            "(there is no CPU or PyTorch fallback for this operator)")
+    lib = ctypes.CDLL(str(LIB_PATH))
+    lib.nvfp4_gemm.argtypes = [ctypes.POINTER(Problem), ctypes.POINTER(GemmConfig), c_void_p]
+    lib.nvfp4_gemm.restype = c_int
+    lib.nvfp4_gemv.argtypes = [ctypes.POINTER(Problem), c_void_p]
+    lib.nvfp4_gemv.restype = c_int
+    lib.nvfp4_matmul.argtypes = [ctypes.POINTER(Problem), c_void_p]
+    lib.nvfp4_matmul.restype = c_int
+    lib.nvfp4_check_status.argtypes = [c_void_p]
+    lib.nvfp4_check_status.restype = c_int
+    lib.nvfp4_set_wait_timeout_ns.argtypes = [c_uint64]
+    lib.nvfp4_set_wait_timeout_ns.restype = c_uint64
+    lib.nvfp4_selftest_bounded_wait.argtypes = [c_void_p]
+    lib.nvfp4_selftest_bounded_wait.restype = c_int
+    lib.nvfp4_scratch_bytes.argtypes = []
+    lib.nvfp4_scratch_bytes.restype = c_size_t
+    lib.nvfp4_plan_units.argtypes = [c_int, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int),
+                                     ctypes.POINTER(c_int), c_int]
+    lib.nvfp4_plan_units.restype = c_int
+    lib.nvfp4_launch_count.argtypes = []
+    lib.nvfp4_launch_count.restype = c_uint64
+    lib.nvfp4_last_kernel.argtypes = []
+    lib.nvfp4_last_kernel.restype = c_char_p
+    lib.nvfp4_shutdown.argtypes = []
+    lib.nvfp4_shutdown.restype = None
+    lib.nvfp4_last_error.argtypes = []
+    lib.nvfp4_last_error.restype = c_char_p
+    lib.nvfp4_version.argtypes = []
+    lib.nvfp4_version.restype = c_char_p
+    _lib = lib
+    return lib
+
+
+def check(rc: int) -> None:
+    if rc != NVFP4_OK:
+        raise Nvfp4Error(rc, load().nvfp4_last_error().decode())

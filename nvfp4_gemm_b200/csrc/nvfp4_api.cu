@@ -1,0 +1,408 @@
+// C ABI of the library (declared in include/nvfp4_b200.h): argument validation, tensor-map
+// cache, per-device scratch, kernel selection and launch.  No allocation, tensor-map encoding
+// or synchronisation happens on the steady-state path of nvfp4_gemm / nvfp4_gemv.
+#include "../../include/nvfp4_b200.h"
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "gemm_sm100.cuh"
+#include "gemv_sm100.cuh"
+
+namespace {
+
+using namespace nvfp4;
+
+thread_local std::string t_error;
+thread_local const char* t_last_kernel = "";
+std::atomic<uint64_t> g_launches{0};
+std::atomic<uint64_t> g_timeout_ns{1000000000ull};
+
+int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    t_error = buf;
+    return code;
+}
+
+#define CUDA_TRY(expr)                                                                             \
+    do {                                                                                           \
+        cudaError_t e__ = (expr);                                                                  \
+        if (e__ != cudaSuccess) return fail(NVFP4_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__)); \
+    } while (0)
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct MapKey {
+    const void* ptr;
+    uint64_t dims[3];
+    uint64_t strides[2];
+    uint32_t box[3];
+    int dtype;
+    bool operator==(const MapKey& o) const { return std::memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapEntry {
+    MapKey key;
+    CUtensorMap map;
+};
+
+constexpr int kMaxGrid = 296;  // scratch slots: two per SM on a 148-SM part
+
+struct DeviceCtx {
+    int device = -1;
+    int num_sms = 0;
+    bool sm100 = false;
+    float* scratch = nullptr;
+    int* counters = nullptr;
+    int* status_host = nullptr;
+    int* status_dev = nullptr;
+    size_t scratch_bytes = 0;
+    std::vector<MapEntry> maps;
+    bool smem_attr_set[8] = {false, false, false, false, false, false, false, false};
+};
+
+std::mutex g_mutex;
+DeviceCtx* g_ctx[64] = {nullptr};
+EncodeTiledFn g_encode = nullptr;
+
+int get_ctx(DeviceCtx** out) {
+    int dev = -1;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(NVFP4_ERR_CUDA, "unexpected device ordinal %d", dev);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (!g_ctx[dev]) {
+        cudaDeviceProp prop;
+        CUDA_TRY(cudaGetDeviceProperties(&prop, dev));
+        DeviceCtx* c = new DeviceCtx();
+        c->device = dev;
+        c->num_sms = prop.multiProcessorCount;
+        c->sm100 = (prop.major == 10);
+        CUDA_TRY(cudaHostAlloc(reinterpret_cast<void**>(&c->status_host), sizeof(int), cudaHostAllocMapped));
+        *c->status_host = 0;
+        CUDA_TRY(cudaHostGetDevicePointer(reinterpret_cast<void**>(&c->status_dev), c->status_host, 0));
+        g_ctx[dev] = c;
+    }
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        if (!fn || qres != cudaDriverEntryPointSuccess)
+            return fail(NVFP4_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+        g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    *out = g_ctx[dev];
+    return NVFP4_OK;
+}
+
+int ensure_scratch(DeviceCtx* c) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (c->scratch) return NVFP4_OK;
+    const size_t bytes = static_cast<size_t>(kMaxGrid) * kBM * 256 * sizeof(float);
+    CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&c->scratch), bytes));
+    CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&c->counters), kMaxGrid * sizeof(int)));
+    CUDA_TRY(cudaMemset(c->scratch, 0, bytes));
+    CUDA_TRY(cudaMemset(c->counters, 0, kMaxGrid * sizeof(int)));
+    CUDA_TRY(cudaDeviceSynchronize());
+    c->scratch_bytes = bytes + kMaxGrid * sizeof(int);
+    return NVFP4_OK;
+}
+
+// Tensor maps are cached by (pointer, extents, strides, box): re-encoding four maps per call,
+// as the reference does (s_128t.py:569-577), costs more than a short GEMM.
+int get_map(DeviceCtx* c, const MapKey& key, CUtensorMapSwizzle swizzle, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    for (const MapEntry& e : c->maps)
+        if (e.key == key) {
+            *out = e.map;
+            return NVFP4_OK;
+        }
+    MapEntry e;
+    std::memset(&e, 0, sizeof(e));
+    e.key = key;
+    cuuint64_t dims[3] = {key.dims[0], key.dims[1], key.dims[2]};
+    cuuint64_t strides[2] = {key.strides[0], key.strides[1]};
+    cuuint32_t box[3] = {key.box[0], key.box[1], key.box[2]};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUresult r = g_encode(&e.map, static_cast<CUtensorMapDataType>(key.dtype), 3, const_cast<void*>(key.ptr), dims, strides,
+                          box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(NVFP4_ERR_CUDA, "cuTensorMapEncodeTiled failed (CUresult %d) dims {%llu,%llu,%llu} strides {%llu,%llu}",
+                    static_cast<int>(r), (unsigned long long)dims[0], (unsigned long long)dims[1],
+                    (unsigned long long)dims[2], (unsigned long long)strides[0], (unsigned long long)strides[1]);
+    if (c->maps.size() >= 256) c->maps.erase(c->maps.begin());
+    c->maps.push_back(e);
+    *out = e.map;
+    return NVFP4_OK;
+}
+
+MapKey make_key(const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s0, uint64_t s1, uint32_t b0, uint32_t b1,
+                int dtype) {
+    MapKey k;
+    std::memset(&k, 0, sizeof(k));
+    k.ptr = ptr;
+    k.dims[0] = d0; k.dims[1] = d1; k.dims[2] = d2;
+    k.strides[0] = s0; k.strides[1] = s1;
+    k.box[0] = b0; k.box[1] = b1; k.box[2] = 1;
+    k.dtype = dtype;
+    return k;
+}
+
+bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+template <int BN, int STAGES, bool TMA_STORE>
+int launch_gemm(DeviceCtx* c, int variant, const GemmParams& params, int grid, cudaStream_t stream, const char* name) {
+    using S = GemmSmem<BN, STAGES, TMA_STORE>;
+    auto kernel = gemm_nvfp4_kernel<BN, STAGES, TMA_STORE>;
+    if (!c->smem_attr_set[variant]) {
+        CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamicBytes));
+        c->smem_attr_set[variant] = true;
+    }
+    kernel<<<grid, kGemmThreads, S::kDynamicBytes, stream>>>(params);
+    CUDA_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    t_last_kernel = name;
+    return NVFP4_OK;
+}
+
+__global__ void bounded_wait_selftest_kernel(int* status, unsigned long long timeout_ns) {
+    __shared__ uint64_t bar;
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(ptx::smem_u32(&bar), 1);
+        abort_flag = 0;
+        ptx::fence_mbar_init();
+        // Nothing ever arrives on this barrier: the wait has to give up by itself.
+        const bool ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar), 0u, &abort_flag, timeout_ns);
+        if (!ok) {
+            *reinterpret_cast<volatile int*>(status) = kStatusWaitTimeout;
+            __threadfence_system();
+        }
+    }
+}
+
+int validate_common(const nvfp4_problem* p) {
+    if (!p) return fail(NVFP4_ERR_INVALID_ARGUMENT, "problem is NULL");
+    if (p->m < 1 || p->n < 1 || p->k < 1 || p->l < 1)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "m, n, k, l must be positive (got %d, %d, %d, %d)", p->m, p->n, p->k, p->l);
+    if (!p->a || !p->b || !p->c) return fail(NVFP4_ERR_INVALID_ARGUMENT, "a, b and c must not be NULL");
+    return NVFP4_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int nvfp4_gemm(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* stream_v) {
+    if (int rc = validate_common(p)) return rc;
+    if (!p->sfa_perm || !p->sfb_perm)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "the GEMM needs the permuted scale tensors (sfa_perm, sfb_perm)");
+    if (p->k % kKPerStage) return fail(NVFP4_ERR_INVALID_ARGUMENT, "k must be a multiple of 256 (got %d)", p->k);
+    if (p->n % 128) return fail(NVFP4_ERR_INVALID_ARGUMENT, "n must be a multiple of 128 (got %d)", p->n);
+    if (!aligned(p->a, 16) || !aligned(p->b, 16) || !aligned(p->c, 16) || !aligned(p->sfa_perm, 16) || !aligned(p->sfb_perm, 16))
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "a, b, c, sfa_perm and sfb_perm must be 16-byte aligned");
+    if (p->a_row_stride % 16 || p->b_row_stride % 16 || p->a_row_stride < p->k / 2 || p->b_row_stride < p->k / 2)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "row strides of a and b must be multiples of 16 bytes and >= k/2");
+    if (p->c_row_stride % 8 || p->c_row_stride < p->n)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "c_row_stride must be a multiple of 8 elements and >= n");
+    if (p->l > 1 && (p->a_batch_stride % 16 || p->b_batch_stride % 16 || p->c_batch_stride % 8 ||
+                     p->sfa_perm_batch_stride % 16 || p->sfb_perm_batch_stride % 16))
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "batch strides must keep 16-byte alignment");
+
+    nvfp4_gemm_config cf = {0, 0, 0, 0};
+    if (cfg) cf = *cfg;
+    if (cf.tile_n != 0 && cf.tile_n != 128 && cf.tile_n != 256)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "tile_n must be 0, 128 or 256");
+    if (cf.epilogue < 0 || cf.epilogue > 2) return fail(NVFP4_ERR_INVALID_ARGUMENT, "epilogue must be 0, 1 or 2");
+    if (cf.cta_group != 0 && cf.cta_group != 1)
+        return fail(NVFP4_ERR_UNSUPPORTED, "cta_group %d is not built", cf.cta_group);
+
+    DeviceCtx* c = nullptr;
+    if (int rc = get_ctx(&c)) return rc;
+    if (!c->sm100) return fail(NVFP4_ERR_UNSUPPORTED, "device %d is not sm_100", c->device);
+    if (int rc = ensure_scratch(c)) return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+    int bn = cf.tile_n;
+    if (bn == 0) bn = (p->n % 256 == 0) ? 256 : 128;
+    if (p->n % bn) return fail(NVFP4_ERR_INVALID_ARGUMENT, "n = %d is not a multiple of tile_n = %d", p->n, bn);
+
+    GemmParams g;
+    std::memset(&g, 0, sizeof(g));
+    g.M = p->m; g.N = p->n; g.K = p->k; g.L = p->l;
+    g.tiles_m = (p->m + kBM - 1) / kBM;
+    g.tiles_n = p->n / bn;
+    g.k_tiles = p->k / kKPerStage;
+    const long long units = static_cast<long long>(g.tiles_m) * g.tiles_n * p->l * g.k_tiles;
+    if (units > 0x7fffffffLL) return fail(NVFP4_ERR_INVALID_ARGUMENT, "problem too large: %lld work units", units);
+    g.total_units = static_cast<int>(units);
+    g.sfa = static_cast<const uint8_t*>(p->sfa_perm);
+    g.sfb = static_cast<const uint8_t*>(p->sfb_perm);
+    g.c = static_cast<__half*>(p->c);
+    g.scratch = c->scratch;
+    g.counters = c->counters;
+    g.status = c->status_dev;
+    g.sfa_batch_stride = p->sfa_perm_batch_stride;
+    g.sfb_batch_stride = p->sfb_perm_batch_stride;
+    g.c_row_stride = p->c_row_stride;
+    g.c_batch_stride = p->c_batch_stride;
+    g.timeout_ns = g_timeout_ns.load();
+
+    int grid = cf.grid > 0 ? cf.grid : c->num_sms;
+    if (grid > kMaxGrid) grid = kMaxGrid;
+    if (grid > g.total_units) grid = g.total_units;
+
+    // TMA-store epilogue when whole tiles dominate (at least two tiles per CTA); otherwise the
+    // deeper ring of the direct-store variant matters more than the store path.
+    int epilogue = cf.epilogue;
+    const long long tiles = static_cast<long long>(g.tiles_m) * g.tiles_n * p->l;
+    if (epilogue == 0) epilogue = (tiles >= 2LL * grid) ? 2 : 1;
+
+    const uint64_t kbytes = static_cast<uint64_t>(p->k) / 2;
+    const uint64_t a_bs = p->l > 1 ? static_cast<uint64_t>(p->a_batch_stride) : static_cast<uint64_t>(p->a_row_stride) * p->m;
+    const uint64_t b_bs = p->l > 1 ? static_cast<uint64_t>(p->b_batch_stride) : static_cast<uint64_t>(p->b_row_stride) * p->n;
+    const uint64_t c_bs = p->l > 1 ? static_cast<uint64_t>(p->c_batch_stride) * 2 : static_cast<uint64_t>(p->c_row_stride) * 2 * p->m;
+    if (int rc = get_map(c, make_key(p->a, kbytes, p->m, p->l, p->a_row_stride, a_bs, kBKBytes, kBM, CU_TENSOR_MAP_DATA_TYPE_UINT8),
+                         CU_TENSOR_MAP_SWIZZLE_128B, &g.tma_a)) return rc;
+    if (int rc = get_map(c, make_key(p->b, kbytes, p->n, p->l, p->b_row_stride, b_bs, kBKBytes, bn, CU_TENSOR_MAP_DATA_TYPE_UINT8),
+                         CU_TENSOR_MAP_SWIZZLE_128B, &g.tma_b)) return rc;
+    if (epilogue == 2) {
+        if (int rc = get_map(c, make_key(p->c, p->n, p->m, p->l, static_cast<uint64_t>(p->c_row_stride) * 2, c_bs, 64, 32,
+                                         CU_TENSOR_MAP_DATA_TYPE_FLOAT16),
+                             CU_TENSOR_MAP_SWIZZLE_128B, &g.tma_c)) return rc;
+    }
+
+    if (bn == 128 && epilogue == 2) return launch_gemm<128, 5, true>(c, 0, g, grid, stream, "gemm_1cta_n128_s5_tmastore");
+    if (bn == 128) return launch_gemm<128, 6, false>(c, 1, g, grid, stream, "gemm_1cta_n128_s6_direct");
+    if (epilogue == 2) return launch_gemm<256, 3, true>(c, 2, g, grid, stream, "gemm_1cta_n256_s3_tmastore");
+    return launch_gemm<256, 4, false>(c, 3, g, grid, stream, "gemm_1cta_n256_s4_direct");
+}
+
+int nvfp4_gemv(const nvfp4_problem* p, void* stream_v) {
+    if (int rc = validate_common(p)) return rc;
+    if (p->n != 1) return fail(NVFP4_ERR_INVALID_ARGUMENT, "the GEMV needs n == 1 (got %d)", p->n);
+    if (!p->sfa || !p->sfb) return fail(NVFP4_ERR_INVALID_ARGUMENT, "the GEMV needs the plain scale tensors (sfa, sfb)");
+    if (p->k % 64) return fail(NVFP4_ERR_INVALID_ARGUMENT, "k must be a multiple of 64 (got %d)", p->k);
+    if (!aligned(p->a, 32) || !aligned(p->b, 32) || !aligned(p->sfa, 4) || !aligned(p->sfb, 4))
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "a and b must be 32-byte aligned, sfa and sfb 4-byte aligned");
+    if (p->a_row_stride % 32 || p->sfa_row_stride % 4 || p->a_row_stride < p->k / 2 || p->sfa_row_stride < p->k / 16)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "a_row_stride must be a multiple of 32 bytes, sfa_row_stride of 4");
+    if (p->l > 1 && (p->a_batch_stride % 32 || p->b_batch_stride % 32 || p->sfa_batch_stride % 4 || p->sfb_batch_stride % 4))
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "batch strides must keep 32-byte (a, b) / 4-byte (sfa, sfb) alignment");
+    if (p->l > 65535) return fail(NVFP4_ERR_INVALID_ARGUMENT, "l must be <= 65535");
+
+    DeviceCtx* c = nullptr;
+    if (int rc = get_ctx(&c)) return rc;
+    if (!c->sm100) return fail(NVFP4_ERR_UNSUPPORTED, "device %d is not sm_100", c->device);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+    GemvParams g;
+    g.a = static_cast<const uint8_t*>(p->a);
+    g.b = static_cast<const uint8_t*>(p->b);
+    g.sfa = static_cast<const uint8_t*>(p->sfa);
+    g.sfb = static_cast<const uint8_t*>(p->sfb);
+    g.c = static_cast<__half*>(p->c);
+    g.a_row_stride = p->a_row_stride; g.a_batch_stride = p->a_batch_stride;
+    g.b_batch_stride = p->b_batch_stride;
+    g.sfa_row_stride = p->sfa_row_stride; g.sfa_batch_stride = p->sfa_batch_stride;
+    g.sfb_batch_stride = p->sfb_batch_stride;
+    g.c_row_stride = p->c_row_stride; g.c_batch_stride = p->c_batch_stride;
+    g.M = p->m; g.K = p->k; g.L = p->l;
+
+    constexpr int R = 2;
+    const int rows_per_cta = kGemvWarps * R;
+    dim3 grid((p->m + rows_per_cta - 1) / rows_per_cta, p->l);
+    gemv_nvfp4_kernel<R><<<grid, kGemvThreads, 0, stream>>>(g);
+    CUDA_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    t_last_kernel = "gemv_warp_r2";
+    return NVFP4_OK;
+}
+
+int nvfp4_matmul(const nvfp4_problem* p, void* stream) {
+    if (p && p->n == 1) return nvfp4_gemv(p, stream);
+    return nvfp4_gemm(p, nullptr, stream);
+}
+
+int nvfp4_check_status(void* stream_v) {
+    DeviceCtx* c = nullptr;
+    if (int rc = get_ctx(&c)) return rc;
+    CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream_v)));
+    const int st = *reinterpret_cast<volatile int*>(c->status_host);
+    if (st == kStatusOk) return NVFP4_OK;
+    *reinterpret_cast<volatile int*>(c->status_host) = 0;
+    // A kernel that gave up may have left partial sums behind: restore the all-zero invariant.
+    if (c->scratch) {
+        CUDA_TRY(cudaDeviceSynchronize());
+        CUDA_TRY(cudaMemset(c->scratch, 0, c->scratch_bytes - kMaxGrid * sizeof(int)));
+        CUDA_TRY(cudaMemset(c->counters, 0, kMaxGrid * sizeof(int)));
+        CUDA_TRY(cudaDeviceSynchronize());
+    }
+    return fail(NVFP4_ERR_DEVICE_TIMEOUT, "a kernel gave up on a bounded wait (device status %d)", st);
+}
+
+uint64_t nvfp4_set_wait_timeout_ns(uint64_t ns) { return g_timeout_ns.exchange(ns); }
+
+int nvfp4_selftest_bounded_wait(void* stream_v) {
+    DeviceCtx* c = nullptr;
+    if (int rc = get_ctx(&c)) return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>(c->status_dev, g_timeout_ns.load());
+    CUDA_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    return nvfp4_check_status(stream_v);
+}
+
+size_t nvfp4_scratch_bytes(void) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    return g_ctx[dev] ? g_ctx[dev]->scratch_bytes : 0;
+}
+
+int nvfp4_plan_units(int total_units, int grid, int cta, int* begin, int* end, int* first_tile_slot, int k_tiles) {
+    if (total_units < 1 || grid < 1 || cta < 0 || cta >= grid || k_tiles < 1 || !begin || !end)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "bad partition query");
+    *begin = unit_boundary(cta, grid, total_units);
+    *end = unit_boundary(cta + 1, grid, total_units);
+    if (first_tile_slot) *first_tile_slot = unit_owner((*begin / k_tiles) * k_tiles, grid, total_units);
+    return NVFP4_OK;
+}
+
+uint64_t nvfp4_launch_count(void) { return g_launches.load(); }
+
+const char* nvfp4_last_kernel(void) { return t_last_kernel; }
+
+void nvfp4_shutdown(void) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    int prev = -1;
+    cudaGetDevice(&prev);
+    for (int d = 0; d < 64; ++d) {
+        DeviceCtx* c = g_ctx[d];
+        if (!c) continue;
+        cudaSetDevice(d);
+        cudaDeviceSynchronize();
+        if (c->scratch) cudaFree(c->scratch);
+        if (c->counters) cudaFree(c->counters);
+        if (c->status_host) cudaFreeHost(c->status_host);
+        delete c;
+        g_ctx[d] = nullptr;
+    }
+    if (prev >= 0) cudaSetDevice(prev);
+}
+
+const char* nvfp4_last_error(void) { return t_error.c_str(); }
+
+const char* nvfp4_version(void) { return "nvfp4_b200 0.1 (sm_100a)"; }
+
+}  // extern "C"

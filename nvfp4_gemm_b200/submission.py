@@ -1,0 +1,95 @@
+"""The operator entry point, with the reference's signature (template.py:4-25):
+
+    custom_kernel(data) -> c,   data = (a, b, sfa, sfb, sfa_permuted, sfb_permuted, c)
+
+``c`` is pre-allocated by the caller, written in place and returned (template.py:20).
+``b.shape[0] == 1`` selects the GEMV (same tuple positions, old_files/1.py:697-698); every
+other shape goes to the tensor-core GEMM, which reads the permuted scale tensors like
+s_128t.py:605-609.  The work is enqueued on torch's current CUDA stream and not waited for.
+All compute happens in the CUDA library behind the C ABI; there is no PyTorch or CPU path.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import GemmConfig, Nvfp4Error, Problem
+from .task import input_t, output_t
+
+
+def _batch_stride(t: torch.Tensor, dim: int = 2) -> int:
+    return t.stride(dim) if t.shape[dim] > 1 else 0
+
+
+def make_problem(data: input_t) -> Problem:
+    """Translate the 7-tuple into the C ABI's ``nvfp4_problem`` (pointers, sizes, strides)."""
+    a, b, sfa, sfb, sfa_perm, sfb_perm, c = data
+    m, k_bytes, l = a.shape
+    n = b.shape[0]
+    if b.shape[1] != k_bytes or b.shape[2] != l:
+        raise ValueError(f"a {tuple(a.shape)} and b {tuple(b.shape)} disagree on k or l")
+    if tuple(c.shape) != (m, n, l):
+        raise ValueError(f"c has shape {tuple(c.shape)}, expected {(m, n, l)}")
+    if a.stride(1) != 1 or b.stride(1) != 1 or c.stride(1) != 1 and n > 1:
+        raise ValueError("a, b must be K-major (stride 1 along k) and c row-major")
+    if a.element_size() != 1 or b.element_size() != 1 or sfa.element_size() != 1 or c.dtype != torch.float16:
+        raise ValueError("expected packed fp4 (1 byte per 2 values), 1-byte scales and fp16 output")
+    p = Problem()
+    p.a, p.b, p.c = a.data_ptr(), b.data_ptr(), c.data_ptr()
+    p.sfa, p.sfb = sfa.data_ptr(), sfb.data_ptr()
+    p.sfa_perm = sfa_perm.data_ptr() if sfa_perm is not None else None
+    p.sfb_perm = sfb_perm.data_ptr() if sfb_perm is not None else None
+    p.m, p.n, p.k, p.l = m, n, 2 * k_bytes, l
+    p.a_row_stride, p.a_batch_stride = a.stride(0), _batch_stride(a)
+    p.b_row_stride, p.b_batch_stride = (b.stride(0) if n > 1 else k_bytes), _batch_stride(b)
+    p.sfa_row_stride, p.sfa_batch_stride = sfa.stride(0), _batch_stride(sfa)
+    p.sfb_row_stride, p.sfb_batch_stride = (sfb.stride(0) if n > 1 else k_bytes // 8), _batch_stride(sfb)
+    # permuted scales: [32, 4, rest_rows, 4, rest_k, L]; the batch is the last dimension
+    p.sfa_perm_batch_stride = _batch_stride(sfa_perm, 5) if sfa_perm is not None else 0
+    p.sfb_perm_batch_stride = _batch_stride(sfb_perm, 5) if sfb_perm is not None else 0
+    p.c_row_stride, p.c_batch_stride = c.stride(0), _batch_stride(c)
+    return p
+
+
+def _require_cuda(data: input_t) -> None:
+    if not all(t.is_cuda for t in data if t is not None):
+        raise ValueError("custom_kernel needs CUDA tensors (there is no CPU fallback)")
+
+
+def custom_kernel(data: input_t) -> output_t:
+    lib = _lib.load()
+    _require_cuda(data)
+    problem = make_problem(data)
+    stream = torch.cuda.current_stream(data[0].device).cuda_stream
+    with torch.cuda.device(data[0].device):
+        _lib.check(lib.nvfp4_matmul(problem, stream))
+    return data[6]
+
+
+def gemm(data: input_t, tile_n: int = 0, epilogue: int = 0, grid: int = 0, cta_group: int = 0) -> output_t:
+    """The GEMM with an explicit kernel configuration (tests and tuning)."""
+    lib = _lib.load()
+    _require_cuda(data)
+    problem = make_problem(data)
+    cfg = GemmConfig(tile_n, epilogue, grid, cta_group)
+    stream = torch.cuda.current_stream(data[0].device).cuda_stream
+    with torch.cuda.device(data[0].device):
+        _lib.check(lib.nvfp4_gemm(problem, cfg, stream))
+    return data[6]
+
+
+def check_status() -> None:
+    """Synchronise the current stream and raise if a kernel reported a timed-out wait."""
+    lib = _lib.load()
+    _lib.check(lib.nvfp4_check_status(torch.cuda.current_stream().cuda_stream))
+
+
+def last_kernel() -> str:
+    return _lib.load().nvfp4_last_kernel().decode()
+
+
+def launch_count() -> int:
+    return int(_lib.load().nvfp4_launch_count())
+
+
+__all__ = ["custom_kernel", "gemm", "check_status", "last_kernel", "launch_count", "make_problem", "Nvfp4Error"]

@@ -1,0 +1,126 @@
+"""GPU parity of the tensor-core GEMM against the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import assert_bit_exact, assert_close, expected_fp16
+
+pytestmark = pytest.mark.gpu
+
+# (m, n, k, l): the reference's test shapes (task.yml:41-51) ...
+TASK_SHAPES = [
+    (128, 256, 256, 1), (128, 1536, 7168, 1), (128, 3072, 1536, 1), (256, 7168, 256, 1), (256, 7168, 2048, 1),
+    (384, 7168, 2304, 1), (512, 512, 7168, 1), (512, 4096, 512, 1), (512, 1536, 7168, 1),
+]
+# ... plus ragged M, batched L, N that only fits the 128-wide tile, and a single k-tile
+EXTRA_SHAPES = [(1, 128, 256, 1), (130, 384, 512, 1), (300, 768, 1536, 2), (128, 128, 256, 3), (257, 640, 1024, 2)]
+
+
+@pytest.fixture(scope="module")
+def sub(lib):
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from nvfp4_gemm_b200 import submission
+    return submission
+
+
+@pytest.mark.parametrize("shape", TASK_SHAPES + EXTRA_SHAPES)
+def test_custom_kernel_matches_oracle_bit_exact(sub, oracle, shape):
+    from nvfp4_gemm_b200.inputs import generate_input
+    m, n, k, l = shape
+    data = generate_input(m, n, k, l, 1111)
+    data[6].view(torch.int16).fill_(0x7fff)        # NaN canary: every element must be written
+    out = sub.custom_kernel(data)
+    sub.check_status()
+    assert out is data[6]
+    # integer-valued products and power-of-two scales: fp32 accumulation is exact, so is parity
+    assert_bit_exact(out, expected_fp16(oracle, data), what=f"{shape} {sub.last_kernel()}")
+
+
+@pytest.mark.parametrize("tile_n,epilogue", [(128, 1), (128, 2), (256, 1), (256, 2)])
+@pytest.mark.parametrize("shape,grid", [((128, 512, 4096, 1), 3), ((300, 768, 1536, 2), 0), ((512, 1024, 1024, 1), 5),
+                                        ((128, 256, 256, 1), 0)])
+def test_every_kernel_variant_and_split_pattern(sub, oracle, tile_n, epilogue, shape, grid):
+    from nvfp4_gemm_b200.inputs import generate_input
+    m, n, k, l = shape
+    data = generate_input(m, n, k, l, 7)
+    data[6].view(torch.int16).fill_(0x7fff)
+    sub.gemm(data, tile_n=tile_n, epilogue=epilogue, grid=grid)
+    sub.check_status()
+    assert_bit_exact(data[6], expected_fp16(oracle, data), what=f"{shape} {sub.last_kernel()} grid={grid}")
+    # run it again: the scratch slots must have been left zeroed by the previous launch
+    data[6].view(torch.int16).fill_(0x7fff)
+    sub.gemm(data, tile_n=tile_n, epilogue=epilogue, grid=grid)
+    sub.check_status()
+    assert_bit_exact(data[6], expected_fp16(oracle, data), what=f"second launch {shape}")
+
+
+def test_largest_reference_test_shape(sub, oracle):
+    from nvfp4_gemm_b200.inputs import generate_input
+    m, n, k, l = 2304, 4608, 7168, 1                 # task.yml:47
+    data = generate_input(m, n, k, l, 1111)
+    out = sub.custom_kernel(data)
+    sub.check_status()
+    # the full oracle would take minutes: check 96 sampled rows against all columns
+    rows = np.random.default_rng(0).choice(m, 96, replace=False)
+    a, b, sfa, sfb = oracle.tensors_to_numpy(data)
+    exp = oracle.ref_gemm_c(a[rows], b, sfa[rows], sfb)
+    assert_bit_exact(out[torch.from_numpy(rows).cuda()], exp, what="2304x4608x7168 sampled rows")
+
+
+def test_general_scales_within_stated_tolerance(sub, oracle):
+    """Arbitrary e4m3 scales and values: not exact any more, must stay inside rtol = atol = 1e-3."""
+    from nvfp4_gemm_b200.inputs import generate_input, permute_scale_factors, SF_DTYPE
+    m, n, k, l = 256, 512, 2048, 1
+    a, b, sfa, sfb, _, _, c = generate_input(m, n, k, l, 3)
+    g = torch.Generator().manual_seed(5)
+    sfa_u8 = torch.randint(0x20, 0x58, (l, m, k // 16), dtype=torch.uint8, generator=g).cuda()
+    sfb_u8 = torch.randint(0x20, 0x58, (l, n, k // 16), dtype=torch.uint8, generator=g).cuda()
+    data = (a, b, sfa_u8.permute(1, 2, 0).view(SF_DTYPE), sfb_u8.permute(1, 2, 0).view(SF_DTYPE),
+            permute_scale_factors(sfa_u8).view(SF_DTYPE), permute_scale_factors(sfb_u8).view(SF_DTYPE), c)
+    out = sub.custom_kernel(data)
+    sub.check_status()
+    an, bn, san, sbn = oracle.tensors_to_numpy(data)
+    exp64 = oracle.ref_gemm(an, bn, san, sbn, accumulate="f64")
+    assert_close(out, exp64, rtol=1e-3, atol=1e-3, what="general scales")
+
+
+def test_decode_shape_full_size_properties(sub, oracle):
+    """128 x 7168 x 16384: sampled columns against the oracle, overflow pattern, and exact linearity
+    (doubling every scale of A doubles C, including the values that overflow to inf)."""
+    from nvfp4_gemm_b200.inputs import generate_input
+    m, n, k, l = 128, 7168, 16384, 1
+    data = generate_input(m, n, k, l, 1111)
+    out = sub.custom_kernel(data).clone()
+    sub.check_status()
+    cols = np.sort(np.random.default_rng(1).choice(n, 256, replace=False))
+    a, b, sfa, sfb = oracle.tensors_to_numpy(data)
+    exp = oracle.ref_gemm_c(a, b[cols], sfa, sfb[cols])
+    assert_bit_exact(out[:, torch.from_numpy(cols).cuda()], exp, what="C1 sampled columns")
+    # linearity: +1 on every exponent of SFA (byte + 8)
+    a_t, b_t, sfa_t, sfb_t, sfap_t, sfbp_t, c_t = data
+    sfap2 = (sfap_t.view(torch.uint8) + 8).view(sfap_t.dtype)
+    out2 = sub.custom_kernel((a_t, b_t, sfa_t, sfb_t, sfap2, sfbp_t, torch.empty_like(c_t)))
+    sub.check_status()
+    assert torch.equal(out2.float(), (out.float() * 2).half().float())
+
+
+def test_prefill_shape_full_size_sampled(sub, oracle):
+    from nvfp4_gemm_b200.inputs import generate_input
+    m, n, k, l = 4096, 7168, 7168, 1
+    data = generate_input(m, n, k, l, 1111)
+    out = sub.custom_kernel(data)
+    sub.check_status()
+    rng = np.random.default_rng(2)
+    rows = np.sort(rng.choice(m, 64, replace=False))
+    cols = np.sort(rng.choice(n, 512, replace=False))
+    a, b, sfa, sfb = oracle.tensors_to_numpy(data)
+    exp = oracle.ref_gemm_c(a[rows], b[cols], sfa[rows], sfb[cols])
+    got = out[torch.from_numpy(rows).cuda()][:, torch.from_numpy(cols).cuda()]
+    assert_bit_exact(got, exp, what="C3 sampled block")
+    # checksum of checksums: column sums of C equal (sum of dequantised A rows) . B^T in fp64
+    aq = oracle.dequantize(a[:, :, 0], sfa[:, :, 0]).astype(np.float64).sum(axis=0)
+    bq = oracle.dequantize(b[cols[:64], :, 0], sfb[cols[:64], :, 0]).astype(np.float64)
+    want = bq @ aq
+    have = out[:, torch.from_numpy(cols[:64]).cuda(), 0].double().sum(dim=0).cpu().numpy()
+    np.testing.assert_allclose(have, want, rtol=2e-3, atol=64.0)   # fp16 rounding of 4096 addends per column

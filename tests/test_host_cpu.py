@@ -1,0 +1,112 @@
+"""Host-side logic that needs no GPU: the C ABI loads and exports what the header declares,
+argument validation, the work partition, and the tuple -> problem translation."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+from nvfp4_gemm_b200 import _lib
+from nvfp4_gemm_b200.inputs import generate_input
+from nvfp4_gemm_b200.submission import custom_kernel, make_problem
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol(lib):
+    header = open(os.path.join(ROOT, "include", "nvfp4_b200.h")).read()
+    declared = set(re.findall(r"\b(nvfp4_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found in the header"
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in include/nvfp4_b200.h but not exported"
+    assert set(_lib.EXPORTED_SYMBOLS) <= declared
+    assert b"sm_100a" in lib.nvfp4_version()
+
+
+def test_make_problem_strides():
+    data = generate_input(256, 384, 512, 2, 1, device="cpu")
+    p = make_problem(data)
+    assert (p.m, p.n, p.k, p.l) == (256, 384, 512, 2)
+    assert p.a_row_stride == 256 and p.a_batch_stride == 256 * 256
+    assert p.b_row_stride == 256 and p.b_batch_stride == 384 * 256
+    assert p.sfa_row_stride == 32 and p.sfa_batch_stride == 256 * 32
+    assert p.sfa_perm_batch_stride == 2 * 8 * 512 and p.sfb_perm_batch_stride == 3 * 8 * 512
+    assert p.c_row_stride == 384 and p.c_batch_stride == 256 * 384
+    gv = make_problem(generate_input(64, 1, 256, 3, 1, device="cpu"))
+    assert gv.n == 1 and gv.c_row_stride == 1 and gv.c_batch_stride == 64 and gv.b_batch_stride == 128
+
+
+def test_custom_kernel_refuses_cpu_tensors(lib):
+    with pytest.raises(ValueError, match="no CPU fallback"):
+        custom_kernel(generate_input(128, 128, 256, 1, 1, device="cpu"))
+
+
+def _problem(**over):
+    data = generate_input(128, 256, 512, 1, 1, device="cpu")
+    p = make_problem(data)
+    for k, v in over.items():
+        setattr(p, k, v)
+    return p, data
+
+
+@pytest.mark.parametrize("over,msg", [
+    (dict(k=300), "multiple of 256"),
+    (dict(n=200), "multiple of 128"),
+    (dict(m=0), "positive"),
+    (dict(a=None), "must not be NULL"),
+    (dict(sfa_perm=None), "permuted scale"),
+    (dict(a_row_stride=250), "row strides"),
+    (dict(c_row_stride=257), "c_row_stride"),
+])
+def test_gemm_rejects_bad_arguments_before_touching_the_gpu(lib, over, msg):
+    p, _keep = _problem(**over)
+    rc = lib.nvfp4_gemm(p, None, None)
+    assert rc == _lib.NVFP4_ERR_INVALID_ARGUMENT
+    assert msg in lib.nvfp4_last_error().decode()
+
+
+def test_gemm_rejects_misaligned_pointer(lib):
+    p, _keep = _problem()
+    p.b = p.b + 8
+    assert lib.nvfp4_gemm(p, None, None) == _lib.NVFP4_ERR_INVALID_ARGUMENT
+    cfg = _lib.GemmConfig(64, 0, 0, 0)
+    p, _keep = _problem()
+    assert lib.nvfp4_gemm(p, cfg, None) == _lib.NVFP4_ERR_INVALID_ARGUMENT
+
+
+def test_gemv_rejects_bad_arguments(lib):
+    data = generate_input(64, 1, 256, 1, 1, device="cpu")
+    p = make_problem(data)
+    p.k = 100
+    assert lib.nvfp4_gemv(p, None) == _lib.NVFP4_ERR_INVALID_ARGUMENT
+    p = make_problem(data)
+    p.n = 2
+    assert lib.nvfp4_gemv(p, None) == _lib.NVFP4_ERR_INVALID_ARGUMENT
+    p = make_problem(data)
+    p.sfa = None
+    assert lib.nvfp4_gemv(p, None) == _lib.NVFP4_ERR_INVALID_ARGUMENT
+
+
+@pytest.mark.parametrize("total,grid,kt", [(3584, 148, 64), (1792, 148, 64), (896 * 28, 148, 28), (7, 7, 1), (100, 148, 4), (229376, 148, 32)])
+def test_work_partition_covers_every_unit_once_and_slots_are_unique(lib, total, grid, kt):
+    grid = min(grid, total)
+    b, e, slot = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    prev_end = 0
+    sizes = []
+    split_tile_slot = {}
+    for cta in range(grid):
+        assert lib.nvfp4_plan_units(total, grid, cta, ctypes.byref(b), ctypes.byref(e), ctypes.byref(slot), kt) == 0
+        assert b.value == prev_end and e.value >= b.value
+        prev_end = e.value
+        sizes.append(e.value - b.value)
+        first_tile = b.value // kt
+        partial = (b.value % kt != 0) or (e.value - b.value < kt)
+        if partial and e.value > b.value:
+            # every CTA touching this tile must agree on its slot
+            assert split_tile_slot.setdefault(first_tile, slot.value) == slot.value
+            assert 0 <= slot.value < grid
+    assert prev_end == total
+    assert max(sizes) - min(sizes) <= 1            # stream-K balance
+    assert len(set(split_tile_slot.values())) == len(split_tile_slot)   # one slot per shared tile
+    assert lib.nvfp4_plan_units(total, grid, grid, ctypes.byref(b), ctypes.byref(e), None, kt) == _lib.NVFP4_ERR_INVALID_ARGUMENT
