@@ -103,8 +103,8 @@ int nvfp4_selftest_bounded_wait(void* stream);
 
 /*
  * Host-side view of the GEMM's work partition (no GPU needed): the half-open range of
- * (tile, k-tile) work units that persistent CTA `cta` of `grid` processes, and the scratch
- * slot used by the first tile it touches if that tile is shared with other CTAs.
+ * (tile, k-tile) work units that persistent worker `cta` of `grid` processes, and the scratch
+ * slot it publishes its first segment to if that segment covers only part of a tile's k-range.
  */
 int nvfp4_plan_units(int total_units, int grid, int cta, int* begin, int* end, int* first_tile_slot, int k_tiles);
 

@@ -1,19 +1,28 @@
 // NVFP4 block-scaled GEMM for sm_100a:  C[M,N] (fp16) = (A x SFA) . (B x SFB)^T.
 //
-// One persistent CTA per SM walks a contiguous range of (output tile, k-tile) work units
-// ("stream-K"): every CTA gets the same number of 128 x BN x 256 units, so small-M decode
-// shapes fill all SMs and large shapes have no partial last wave.  A tile whose k-range is
-// covered by one CTA is written straight to C; a tile shared by several CTAs is summed in an
-// fp32 scratch slot with vector reductions and converted by whichever CTA finishes it.
+// Persistent workers walk a contiguous range of (output tile, k-tile) work units ("stream-K"):
+// every worker gets the same number of units, so small-M decode shapes fill all SMs and large
+// shapes have no partial last wave.  A tile whose k-range one worker covers is written straight
+// to C.  A tile shared by several workers is published as fp32 partials in per-worker scratch
+// slots; whichever worker completes the tile's k-tile count sums the partials in a fixed order
+// (deterministic) and writes fp16.
 //
-// Warp roles (192 threads):
+// A worker is one CTA (CG = 1: 128 x BN tile) or a CTA pair running tcgen05 with cta_group::2
+// (CG = 2: 256 x BN tile; each CTA holds 128 rows of A, BN/2 rows of B and its own 128
+// accumulator rows, so B crosses L2 -> SM once per pair).
+//
+// Warp roles (192 threads per CTA):
 //   warp 0      TMA producer: A/B tiles (128-byte swizzle) and the 512-byte scale atoms of the
 //               permuted layout into a STAGES-deep shared-memory ring (full/empty mbarriers)
-//   warp 1      TMEM owner and MMA issuer: tcgen05.cp scale atoms -> TMEM, four
-//               tcgen05.mma.kind::mxf4nvf4.block_scale (K = 64 each) per stage,
-//               tcgen05.commit to release the stage / publish the accumulator
+//   warp 1      TMEM owner.  Leader CTA: MMA issuer -- tcgen05.cp scale atoms -> TMEM, four
+//               tcgen05.mma.kind::mxf4nvf4.block_scale (K = 64 each) per stage, tcgen05.commit
+//               to release the stage / publish the accumulator.  Second CTA of a pair: relays
+//               "my stage landed" to the leader's peer_full barriers.
 //   warps 2..5  epilogue: tcgen05.ld -> fp16 -> TMA store (or 16-byte stores), or the fp32
-//               partial-tile reduction
+//               partial-tile path
+//
+// No load in this file uses cluster multicast; the only cluster-wide signals are mbarrier
+// arrivals (remote arrive, tcgen05.commit to both CTAs of a pair).
 //
 // Replaces the reference's single-stage, fully serialised kernel (s_128t.py:375-466).
 #pragma once
@@ -21,7 +30,7 @@
 
 namespace nvfp4 {
 
-constexpr int kBM = 128;           // tile rows = TMEM lanes
+constexpr int kBM = 128;           // rows per CTA tile = TMEM lanes
 constexpr int kBKBytes = 128;      // bytes of K per stage row = one 128-byte swizzle row = 256 e2m1
 constexpr int kKPerStage = 256;    // K elements per stage
 constexpr int kMmaPerStage = 4;    // K = 64 per tcgen05.mma
@@ -37,27 +46,32 @@ enum GemmStatus : int {
 };
 
 struct GemmParams {
-    CUtensorMap tma_a;   // {K/2 bytes, M rows, L}, box {128, 128, 1}, 128B swizzle
-    CUtensorMap tma_b;   // {K/2 bytes, N rows, L}, box {128, BN, 1},  128B swizzle
+    CUtensorMap tma_a;   // {K/2 bytes, M rows, L}, box {128, 128, 1},    128B swizzle
+    CUtensorMap tma_b;   // {K/2 bytes, N rows, L}, box {128, BN/CG, 1},  128B swizzle
     CUtensorMap tma_c;   // {N, M, L} fp16, box {64, 32, 1}, 128B swizzle (TMA-store epilogue)
     const uint8_t* sfa;  // permuted scales of A
     const uint8_t* sfb;  // permuted scales of B
     __half* c;
-    float* scratch;      // [grid][BN/4][128][4] fp32 partial-tile slots, all zero between launches
-    int* counters;       // [grid] k-tiles accumulated per slot, all zero between launches
+    float* scratch;      // partial-tile slots [worker][head|tail][cta of pair][BN/4][128][4] fp32
+    int* counters;       // [worker][cta of pair] k-tiles published per shared tile; zero between launches
     int* status;         // host-visible status word
     long long sfa_batch_stride, sfb_batch_stride;  // bytes
     long long c_row_stride, c_batch_stride;        // elements
-    unsigned long long timeout_ns;
+    unsigned long long timeout_cycles;  // limit of every in-kernel wait, in SM clock cycles
+#ifdef NVFP4_TRACE
+    unsigned long long* trace;  // [grid][8] cycle counters (development builds only)
+    int dbg_flags;              // 1: skip scale copies, 2: skip MMA and copies, 4: skip scale loads
+#endif
     int M, N, K, L;
-    int tiles_m, tiles_n, k_tiles;  // k_tiles = K / 256
+    int tiles_m, tiles_n, k_tiles;  // tiles of (128*CG) x BN; k_tiles = K / 256
     int total_units;                // tiles_m * tiles_n * L * k_tiles
 };
 
-template <int BN, int STAGES, bool TMA_STORE>
+template <int CG, int BN, int STAGES, bool TMA_STORE>
 struct GemmSmem {
+    static constexpr uint32_t kBRows = BN / CG;
     static constexpr uint32_t kABytes = kBM * kBKBytes;
-    static constexpr uint32_t kBBytes = BN * kBKBytes;
+    static constexpr uint32_t kBBytes = kBRows * kBKBytes;
     static constexpr uint32_t kSfaBytes = kMmaPerStage * kSfAtomBytes;
     static constexpr uint32_t kSfbBytes = (BN / 128) * kMmaPerStage * kSfAtomBytes;
     static constexpr uint32_t kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
@@ -65,30 +79,54 @@ struct GemmSmem {
     static constexpr uint32_t kStagingOff = STAGES * kStageBytes;
     static constexpr uint32_t kBarOff = kStagingOff + 4 * kStagingPerWarp;
     static constexpr uint32_t kNumAcc = (BN <= 128) ? 2 : 1;
-    // full[STAGES] empty[STAGES] acc_full[2] acc_empty[2] | tmem slot | abort flag | finisher flag
-    static constexpr uint32_t kBytes = kBarOff + (2 * STAGES + 4) * 8 + 16;
+    // full[STAGES] empty[STAGES] peer_full[STAGES] acc_full[2] acc_empty[2] | tmem slot | abort | finisher
+    static constexpr uint32_t kNumBars = 3 * STAGES + 4;
+    static constexpr uint32_t kBytes = kBarOff + kNumBars * 8 + 16;
     static constexpr uint32_t kDynamicBytes = kBytes + 1024;  // slack for manual 1024-byte alignment
     static_assert(kStageBytes % 1024 == 0, "stage tiles must keep 1024-byte alignment");
+    static_assert(kDynamicBytes <= 232448, "exceeds the 227 KB of shared memory one CTA may use");
 };
 
-// Work range of CTA `cta` out of `grid`: units [begin, end).
-__host__ __device__ inline int unit_boundary(int cta, int grid, int total_units) {
-    return static_cast<int>((static_cast<long long>(cta) * total_units) / grid);
+// Work range of worker `w` out of `n`: units [boundary(w), boundary(w + 1)).
+__host__ __device__ inline int unit_boundary(int w, int n, int total_units) {
+    return static_cast<int>((static_cast<long long>(w) * total_units) / n);
 }
-// The CTA whose range holds unit u.
-__host__ __device__ inline int unit_owner(int u, int grid, int total_units) {
-    int c = static_cast<int>((static_cast<long long>(u) * grid) / total_units);
-    if (c >= grid) c = grid - 1;
-    while (c + 1 < grid && unit_boundary(c + 1, grid, total_units) <= u) ++c;
-    while (c > 0 && unit_boundary(c, grid, total_units) > u) --c;
+// The worker whose range holds unit u.
+__host__ __device__ inline int unit_owner(int u, int n, int total_units) {
+    int c = static_cast<int>((static_cast<long long>(u) * n) / total_units);
+    if (c >= n) c = n - 1;
+    while (c + 1 < n && unit_boundary(c + 1, n, total_units) <= u) ++c;
+    while (c > 0 && unit_boundary(c, n, total_units) > u) --c;
     return c;
 }
+// Scratch slot of a worker's partial segment: a worker has at most one segment that starts
+// inside a tile ("head", k0 > 0) and at most one that starts a tile but does not finish it.
+__host__ __device__ inline int partial_slot(int worker, int k0, int cg, int cta_rank) {
+    return (worker * 2 + (k0 > 0 ? 0 : 1)) * cg + cta_rank;
+}
 
-template <int BN, int STAGES, bool TMA_STORE>
+__device__ __forceinline__ uint4 pack8_fp16(const float* v) {
+    uint4 q;
+    __half2 h;
+    h = __floats2half2_rn(v[0], v[1]); q.x = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2half2_rn(v[2], v[3]); q.y = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2half2_rn(v[4], v[5]); q.z = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2half2_rn(v[6], v[7]); q.w = *reinterpret_cast<uint32_t*>(&h);
+    return q;
+}
+__device__ __forceinline__ uint4 pack8_fp16(const uint32_t* v) {
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[i]);
+    return pack8_fp16(f);
+}
+
+template <int CG, int BN, int STAGES, bool TMA_STORE>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __grid_constant__ GemmParams p) {
-    using S = GemmSmem<BN, STAGES, TMA_STORE>;
+    using S = GemmSmem<CG, BN, STAGES, TMA_STORE>;
     constexpr int kNumAcc = S::kNumAcc;
     constexpr int kSfbColsPerMma = BN / 32;  // 4 TMEM columns per 128 rows of B
+    constexpr int kBRows = S::kBRows;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -96,24 +134,28 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
 
     const uint32_t bar_full = smem_base + S::kBarOff;
     const uint32_t bar_empty = bar_full + STAGES * 8;
-    const uint32_t bar_acc_full = bar_empty + STAGES * 8;
+    const uint32_t bar_peer_full = bar_empty + STAGES * 8;
+    const uint32_t bar_acc_full = bar_peer_full + STAGES * 8;
     const uint32_t bar_acc_empty = bar_acc_full + 2 * 8;
     const uint32_t tmem_slot = bar_acc_empty + 2 * 8;
-    volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + S::kBarOff + (2 * STAGES + 4) * 8);
+    volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + S::kBarOff + S::kNumBars * 8);
     volatile uint32_t* abort_flag = tmem_slot_gen + 1;
     volatile uint32_t* finisher_flag = tmem_slot_gen + 2;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const int cta_rank = (CG == 2) ? static_cast<int>(ptx::cluster_ctarank()) : 0;
+    const bool leader = (cta_rank == 0);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             ptx::mbar_init(bar_full + s * 8, 1);
             ptx::mbar_init(bar_empty + s * 8, 1);
+            ptx::mbar_init(bar_peer_full + s * 8, 1);
         }
         for (int a = 0; a < 2; ++a) {
             ptx::mbar_init(bar_acc_full + a * 8, 1);
-            ptx::mbar_init(bar_acc_empty + a * 8, 128);
+            ptx::mbar_init(bar_acc_empty + a * 8, 128 * CG);
         }
         *abort_flag = 0u;
         *finisher_flag = 0u;
@@ -122,68 +164,105 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
         ptx::prefetch_tensormap(&p.tma_b);
         if (TMA_STORE) ptx::prefetch_tensormap(&p.tma_c);
     }
+    if constexpr (CG == 2) {
+        // both CTAs of the pair are resident and have initialised their barriers before any
+        // pair-wide instruction or remote arrival is issued
+        __syncthreads();
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+    }
     if (warp == 1) {
-        ptx::tmem_alloc<1>(tmem_slot, kTmemCols);
-        ptx::tmem_relinquish<1>();
+        ptx::tmem_alloc<CG>(tmem_slot, kTmemCols);
+        ptx::tmem_relinquish<CG>();
     }
     ptx::tc_fence_before();
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_gen;
 
-    const int grid = gridDim.x;
-    const int u_begin = unit_boundary(blockIdx.x, grid, p.total_units);
-    const int u_end = unit_boundary(blockIdx.x + 1, grid, p.total_units);
+    const int n_workers = gridDim.x / CG;
+    const int worker = blockIdx.x / CG;
+    const int u_begin = unit_boundary(worker, n_workers, p.total_units);
+    const int u_end = unit_boundary(worker + 1, n_workers, p.total_units);
     const int KT = p.k_tiles;
     const int sf_kblocks = p.K / 64;  // scale atoms per 128-row block
-    const uint64_t timeout = p.timeout_ns;
+    const uint64_t timeout = p.timeout_cycles;
+#ifdef NVFP4_TRACE
+    const long long trace_t_start = clock64();
+    long long trace_wait = 0, trace_wait2 = 0;
+#define NVFP4_TRACE_BEGIN() const long long trace_t0 = clock64()
+#define NVFP4_TRACE_END(acc) acc += clock64() - trace_t0
+#else
+#define NVFP4_TRACE_BEGIN()
+#define NVFP4_TRACE_END(acc)
+#endif
 
+    // Warps 0 and 1 run their loops with all 32 lanes converged and hand the single-thread
+    // instructions (TMA, tcgen05) to one lane chosen by elect.sync: the compiler then knows the
+    // issuing path is warp-uniform and feeds the descriptors straight from uniform registers.
+    // (Issuing from "if (lane == 0)" costs ~50 cycles per instruction instead.)
     if (warp == 0) {
         // ------------------------------------------------------------ producer
-        if (lane == 0) {
-            // A is re-read by every n-tile (keep it in L2); B streams through once per m-tile.
-            const uint64_t pol_a = ptx::policy_evict_last();
-            const uint64_t pol_b = (p.tiles_m <= 2) ? ptx::policy_evict_first() : ptx::policy_evict_last();
-            uint32_t stage = 0, phase = 0;
-            bool ok = true;
-            for (int u = u_begin; u < u_end && ok;) {
-                const int tile = u / KT;
-                const int k0 = u - tile * KT;
-                const int k1 = min(KT, k0 + (u_end - u));
-                const int nb = tile % p.tiles_n;
-                const int mb = (tile / p.tiles_n) % p.tiles_m;
-                const int l = tile / (p.tiles_n * p.tiles_m);
-                const uint8_t* sfa_tile = p.sfa + l * p.sfa_batch_stride + static_cast<long long>(mb) * sf_kblocks * kSfAtomBytes;
-                const uint8_t* sfb_tile = p.sfb + l * p.sfb_batch_stride +
-                                          static_cast<long long>(nb) * (BN / 128) * sf_kblocks * kSfAtomBytes;
-                for (int kt = k0; kt < k1; ++kt) {
-                    if (!ptx::mbar_wait_bounded(bar_empty + stage * 8, phase ^ 1u, abort_flag, timeout)) {
-                        ok = false;
-                        break;
-                    }
+        // A is re-read by every n-tile (keep it in L2); B streams through once per m-tile.
+        const uint64_t pol_a = ptx::policy_evict_last();
+        const uint64_t pol_b = (p.tiles_m * CG <= 2) ? ptx::policy_evict_first() : ptx::policy_evict_last();
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        for (int u = u_begin; u < u_end && ok;) {
+            const int tile = u / KT;
+            const int k0 = u - tile * KT;
+            const int k1 = min(KT, k0 + (u_end - u));
+            const int nb = tile % p.tiles_n;
+            const int mb = ((tile / p.tiles_n) % p.tiles_m) * CG + cta_rank;  // 128-row block of this CTA
+            const int l = tile / (p.tiles_n * p.tiles_m);
+            const uint8_t* sfa_tile = p.sfa + l * p.sfa_batch_stride + static_cast<long long>(mb) * sf_kblocks * kSfAtomBytes;
+            const uint8_t* sfb_tile = p.sfb + l * p.sfb_batch_stride +
+                                      static_cast<long long>(nb) * (BN / 128) * sf_kblocks * kSfAtomBytes;
+            for (int kt = k0; kt < k1; ++kt) {
+                {
+                    NVFP4_TRACE_BEGIN();
+                    ok = ptx::mbar_wait_bounded<CG == 2>(bar_empty + stage * 8, phase ^ 1u, abort_flag, timeout);
+                    ok = __all_sync(0xffffffffu, ok);
+                    NVFP4_TRACE_END(trace_wait);
+                }
+                if (!ok) break;
+                if (ptx::elect_one()) {
                     const uint32_t full = bar_full + stage * 8;
                     const uint32_t sa = smem_base + stage * S::kStageBytes;
                     const uint32_t sb = sa + S::kABytes;
                     const uint32_t ssfa = sb + S::kBBytes;
                     const uint32_t ssfb = ssfa + S::kSfaBytes;
-                    ptx::mbar_expect_tx(full, S::kStageBytes);
-                    ptx::tma_load_3d(sa, &p.tma_a, kt * kBKBytes, mb * kBM, l, full, pol_a);
-                    ptx::tma_load_3d(sb, &p.tma_b, kt * kBKBytes, nb * BN, l, full, pol_b);
-                    ptx::bulk_load(ssfa, sfa_tile + static_cast<long long>(kt) * S::kSfaBytes, S::kSfaBytes, full);
+#ifdef NVFP4_TRACE
+                    if (p.dbg_flags & 4) {
+                        ptx::mbar_expect_tx(full, S::kABytes + S::kBBytes);
+                        ptx::tma_load_3d(sa, &p.tma_a, kt * kBKBytes, mb * kBM, l, full, pol_a);
+                        ptx::tma_load_3d(sb, &p.tma_b, kt * kBKBytes, nb * BN + cta_rank * kBRows, l, full, pol_b);
+                    } else
+#endif
+                    {
+                        ptx::mbar_expect_tx(full, S::kStageBytes);
+                        ptx::tma_load_3d(sa, &p.tma_a, kt * kBKBytes, mb * kBM, l, full, pol_a);
+                        ptx::tma_load_3d(sb, &p.tma_b, kt * kBKBytes, nb * BN + cta_rank * kBRows, l, full, pol_b);
+                        ptx::bulk_load(ssfa, sfa_tile + static_cast<long long>(kt) * S::kSfaBytes, S::kSfaBytes, full);
 #pragma unroll
-                    for (int h = 0; h < BN / 128; ++h)
-                        ptx::bulk_load(ssfb + h * S::kSfaBytes,
-                                       sfb_tile + (static_cast<long long>(h) * sf_kblocks + kt * kMmaPerStage) * kSfAtomBytes,
-                                       S::kSfaBytes, full);
-                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                        for (int h = 0; h < BN / 128; ++h)
+                            ptx::bulk_load(ssfb + h * S::kSfaBytes,
+                                           sfb_tile + (static_cast<long long>(h) * sf_kblocks + kt * kMmaPerStage) * kSfAtomBytes,
+                                           S::kSfaBytes, full);
+                    }
                 }
-                u += k1 - k0;
+                __syncwarp();
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
+            u += k1 - k0;
         }
+#ifdef NVFP4_TRACE
+        if (lane == 0) p.trace[blockIdx.x * 8 + 1] = trace_wait;
+#endif
     } else if (warp == 1) {
-        // ---------------------------------------------------------- MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = ptx::idesc_nvf4(kBM, BN);
+        if (leader) {
+            // ------------------------------------------------------ MMA issuer
+            constexpr uint32_t idesc = ptx::idesc_nvf4(kBM * CG, BN);
             uint32_t stage = 0, phase = 0, acc_it = 0, sf_it = 0;
             bool ok = true;
             for (int u = u_begin; u < u_end && ok;) {
@@ -192,46 +271,104 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                 const int k1 = min(KT, k0 + (u_end - u));
                 const uint32_t acc = acc_it % kNumAcc;
                 const uint32_t acc_phase = (acc_it / kNumAcc) & 1u;
-                if (!ptx::mbar_wait_bounded(bar_acc_empty + acc * 8, acc_phase ^ 1u, abort_flag, timeout)) break;
+                {
+                    NVFP4_TRACE_BEGIN();
+                    ok = ptx::mbar_wait_bounded<CG == 2>(bar_acc_empty + acc * 8, acc_phase ^ 1u, abort_flag, timeout);
+                    ok = __all_sync(0xffffffffu, ok);
+                    NVFP4_TRACE_END(trace_wait2);
+                }
+                if (!ok) break;
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for (int kt = k0; kt < k1; ++kt) {
-                    if (!ptx::mbar_wait_bounded(bar_full + stage * 8, phase, abort_flag, timeout)) {
-                        ok = false;
-                        break;
+                    {
+                        NVFP4_TRACE_BEGIN();
+                        ok = ptx::mbar_wait_bounded(bar_full + stage * 8, phase, abort_flag, timeout);
+                        if constexpr (CG == 2)
+                            ok = ok && ptx::mbar_wait_bounded<true>(bar_peer_full + stage * 8, phase, abort_flag, timeout);
+                        ok = __all_sync(0xffffffffu, ok);
+                        NVFP4_TRACE_END(trace_wait);
                     }
+                    if (!ok) break;
                     ptx::tc_fence_after();
-                    const uint32_t sa = smem_base + stage * S::kStageBytes;
-                    const uint32_t sb = sa + S::kABytes;
-                    const uint32_t ssfa = sb + S::kBBytes;
-                    const uint32_t ssfb = ssfa + S::kSfaBytes;
-                    const uint32_t sf_buf = sf_it & 1u;
-                    const uint32_t t_sfa = tmem_base + kSfaCol + sf_buf * 16;
-                    const uint32_t t_sfb = tmem_base + kSfbCol + sf_buf * (kMmaPerStage * kSfbColsPerMma);
+                    if (ptx::elect_one()) {
+#ifdef NVFP4_TRACE
+                        if (p.dbg_flags & 2) {  // no tensor work at all: hand the stage straight back
+                            if constexpr (CG == 2) ptx::tc_commit_pair(bar_empty + stage * 8, 0x3);
+                            else ptx::tc_commit(bar_empty + stage * 8);
+                        } else
+#endif
+                        {
+                            const uint32_t sa = smem_base + stage * S::kStageBytes;
+                            const uint32_t sb = sa + S::kABytes;
+                            const uint32_t ssfa = sb + S::kBBytes;
+                            const uint32_t ssfb = ssfa + S::kSfaBytes;
+                            const uint32_t sf_buf = sf_it & 1u;
+                            const uint32_t t_sfa = tmem_base + kSfaCol + sf_buf * 16;
+                            const uint32_t t_sfb = tmem_base + kSfbCol + sf_buf * (kMmaPerStage * kSfbColsPerMma);
+                            // With cta_group::2 each of these runs in both CTAs of the pair, every CTA
+                            // reading its own shared memory at the same offsets.
+#ifdef NVFP4_TRACE
+                            if (!(p.dbg_flags & 1))
+#endif
 #pragma unroll
-                    for (int kb = 0; kb < kMmaPerStage; ++kb) {
-                        ptx::tc_cp_sf<1>(t_sfa + kb * 4, ptx::smem_desc_sf(ssfa + kb * kSfAtomBytes));
+                            for (int kb = 0; kb < kMmaPerStage; ++kb) {
+                                ptx::tc_cp_sf<CG>(t_sfa + kb * 4, ptx::smem_desc_sf(ssfa + kb * kSfAtomBytes));
 #pragma unroll
-                        for (int h = 0; h < BN / 128; ++h)
-                            ptx::tc_cp_sf<1>(t_sfb + kb * kSfbColsPerMma + h * 4,
-                                             ptx::smem_desc_sf(ssfb + h * S::kSfaBytes + kb * kSfAtomBytes));
+                                for (int h = 0; h < BN / 128; ++h)
+                                    ptx::tc_cp_sf<CG>(t_sfb + kb * kSfbColsPerMma + h * 4,
+                                                      ptx::smem_desc_sf(ssfb + h * S::kSfaBytes + kb * kSfAtomBytes));
+                            }
+                            const uint64_t a_desc = ptx::smem_desc_sw128(sa);
+                            const uint64_t b_desc = ptx::smem_desc_sw128(sb);
+#pragma unroll
+                            for (int kb = 0; kb < kMmaPerStage; ++kb) {
+                                // K advances 64 elements = 32 bytes inside the 128-byte swizzle row: +2 in
+                                // the (address >> 4) field of the descriptors.
+                                ptx::tc_mma_nvf4<CG>(d_tmem, a_desc + 2 * kb, b_desc + 2 * kb, idesc, t_sfa + kb * 4,
+                                                     t_sfb + kb * kSfbColsPerMma, (kt > k0 || kb > 0) ? 1u : 0u);
+                            }
+                            // the stage is reusable (in both CTAs) once these MMAs and copies retire
+                            if constexpr (CG == 2) ptx::tc_commit_pair(bar_empty + stage * 8, 0x3);
+                            else ptx::tc_commit(bar_empty + stage * 8);
+                            if (kt == k1 - 1) {  // last k-tile of the segment: publish the accumulator
+                                if constexpr (CG == 2) ptx::tc_commit_pair(bar_acc_full + acc * 8, 0x3);
+                                else ptx::tc_commit(bar_acc_full + acc * 8);
+                            }
+                        }
                     }
-                    const uint64_t a_desc = ptx::smem_desc_sw128(sa);
-                    const uint64_t b_desc = ptx::smem_desc_sw128(sb);
-#pragma unroll
-                    for (int kb = 0; kb < kMmaPerStage; ++kb) {
-                        // K advances 64 elements = 32 bytes inside the 128-byte swizzle row: +2 in the
-                        // (address >> 4) field of the descriptors.
-                        ptx::tc_mma_nvf4<1>(d_tmem, a_desc + 2 * kb, b_desc + 2 * kb, idesc, t_sfa + kb * 4,
-                                            t_sfb + kb * kSfbColsPerMma, (kt > k0 || kb > 0) ? 1u : 0u);
-                    }
-                    ptx::tc_commit(bar_empty + stage * 8);  // stage reusable once these MMAs (and copies) retire
+                    __syncwarp();
                     ++sf_it;
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
-                if (ok) ptx::tc_commit(bar_acc_full + acc * 8);
+#ifdef NVFP4_TRACE
+                if ((p.dbg_flags & 2) && ok && ptx::elect_one()) {
+                    if constexpr (CG == 2) ptx::tc_commit_pair(bar_acc_full + acc * 8, 0x3);
+                    else ptx::tc_commit(bar_acc_full + acc * 8);
+                }
+                __syncwarp();
+#endif
                 ++acc_it;
                 u += k1 - k0;
+            }
+#ifdef NVFP4_TRACE
+            if (lane == 0) {
+                p.trace[blockIdx.x * 8 + 2] = trace_wait;
+                p.trace[blockIdx.x * 8 + 3] = trace_wait2;
+                p.trace[blockIdx.x * 8 + 0] = clock64() - trace_t_start;
+            }
+#endif
+        } else {
+            // ----------------------------------- second CTA of a pair: stage relay
+            uint32_t stage = 0, phase = 0;
+            const int n_stages_total = u_end - u_begin;
+            for (int i = 0; i < n_stages_total; ++i) {
+                bool ok = ptx::mbar_wait_bounded(bar_full + stage * 8, phase, abort_flag, timeout);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                if (lane == 0) ptx::mbar_arrive_cluster(bar_peer_full + stage * 8, 0);
+                __syncwarp();
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
         }
     } else {
@@ -246,19 +383,30 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
             const int k0 = u - tile * KT;
             const int k1 = min(KT, k0 + (u_end - u));
             const int nb = tile % p.tiles_n;
-            const int mb = (tile / p.tiles_n) % p.tiles_m;
+            const int mb = ((tile / p.tiles_n) % p.tiles_m) * CG + cta_rank;
             const int l = tile / (p.tiles_n * p.tiles_m);
             const uint32_t acc = acc_it % kNumAcc;
             const uint32_t acc_phase = (acc_it / kNumAcc) & 1u;
             // All 128 epilogue threads take the same branch: the outcome of the wait is agreed on
             // through a barrier, so a thread that gave up cannot strand the others at a later one.
-            const bool got_acc = ptx::mbar_wait_bounded(bar_acc_full + acc * 8, acc_phase, abort_flag, timeout);
+            bool got_acc;
+            {
+                NVFP4_TRACE_BEGIN();
+                got_acc = ptx::mbar_wait_bounded<CG == 2>(bar_acc_full + acc * 8, acc_phase, abort_flag, timeout);
+                NVFP4_TRACE_END(trace_wait);
+            }
             if (!ptx::named_bar_and(2, 128, got_acc)) break;
+            NVFP4_TRACE_BEGIN();
             ptx::tc_fence_after();
             const uint32_t t_acc = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
             const bool whole_tile = (k1 - k0 == KT);
             const int row = mb * kBM + row_in_tile;
             __half* c_row = p.c + l * p.c_batch_stride + static_cast<long long>(row) * p.c_row_stride + nb * BN;
+            auto release_acc = [&]() {
+                ptx::tc_fence_before();
+                if (CG == 2 && !leader) ptx::mbar_arrive_cluster(bar_acc_empty + acc * 8, 0);
+                else ptx::mbar_arrive(bar_acc_empty + acc * 8);
+            };
 
             if (whole_tile) {
                 if constexpr (TMA_STORE) {
@@ -276,19 +424,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                         __syncwarp();
                         uint8_t* buf = staging_gen + store_buf * 4096 + lane * 128;
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const uint32_t* src = &v[j >> 2][(j & 3) * 8];
-                            uint4 q;
-                            __half2 h;
-                            h = __floats2half2_rn(__uint_as_float(src[0]), __uint_as_float(src[1])); q.x = *reinterpret_cast<uint32_t*>(&h);
-                            h = __floats2half2_rn(__uint_as_float(src[2]), __uint_as_float(src[3])); q.y = *reinterpret_cast<uint32_t*>(&h);
-                            h = __floats2half2_rn(__uint_as_float(src[4]), __uint_as_float(src[5])); q.z = *reinterpret_cast<uint32_t*>(&h);
-                            h = __floats2half2_rn(__uint_as_float(src[6]), __uint_as_float(src[7])); q.w = *reinterpret_cast<uint32_t*>(&h);
-                            *reinterpret_cast<uint4*>(buf + ((j ^ (lane & 7)) << 4)) = q;  // 128-byte swizzle
-                        }
+                        for (int j = 0; j < 8; ++j)  // 16-byte pieces, 128-byte swizzle
+                            *reinterpret_cast<uint4*>(buf + ((j ^ (lane & 7)) << 4)) = pack8_fp16(&v[j >> 2][(j & 3) * 8]);
                         ptx::fence_proxy_async_smem();
                         __syncwarp();
-                        if (lane == 0 && mb * kBM + quad * 32 < p.M) {  // rows past M inside the box are clipped
+                        if (lane == 0 && mb * kBM + quad * 32 < p.M) {  // rows past M inside the box are clipped; one fixed lane owns the bulk groups
                             ptx::tma_store_3d(&p.tma_c, staging + store_buf * 4096, nb * BN + c0, mb * kBM + quad * 32, l);
                             ptx::bulk_commit_group();
                         }
@@ -302,25 +442,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                         ptx::tc_wait_ld();
                         if (row < p.M) {
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                uint4 q;
-                                __half2 h;
-                                h = __floats2half2_rn(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1])); q.x = *reinterpret_cast<uint32_t*>(&h);
-                                h = __floats2half2_rn(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3])); q.y = *reinterpret_cast<uint32_t*>(&h);
-                                h = __floats2half2_rn(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5])); q.z = *reinterpret_cast<uint32_t*>(&h);
-                                h = __floats2half2_rn(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7])); q.w = *reinterpret_cast<uint32_t*>(&h);
-                                *reinterpret_cast<uint4*>(c_row + c0 + 8 * j) = q;
-                            }
+                            for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(c_row + c0 + 8 * j) = pack8_fp16(&v[8 * j]);
                         }
                     }
                 }
-                ptx::tc_fence_before();
-                ptx::mbar_arrive(bar_acc_empty + acc * 8);
+                release_acc();
             } else {
-                // Partial tile: add this CTA's k-range into the tile's fp32 slot.  Slot layout
-                // [BN/4][128 rows][4] keeps each warp's 16-byte reductions contiguous (512 bytes).
-                const int slot = unit_owner(tile * KT, grid, p.total_units);
-                float* slot_base = p.scratch + static_cast<long long>(slot) * (kBM * BN);
+                // Partial tile: publish this worker's k-range as fp32 in its own slot.  Slot layout
+                // [BN/4][128 rows][4] keeps every warp-wide 16-byte access contiguous (512 bytes).
+                float* my_slot = p.scratch + static_cast<long long>(partial_slot(worker, k0, CG, cta_rank)) * (kBM * BN);
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 32) {
                     uint32_t v[32];
@@ -328,46 +458,84 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                     ptx::tc_wait_ld();
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
-                        ptx::red_add_v4(slot_base + ((c0 / 4 + j) * kBM + row_in_tile) * 4, __uint_as_float(v[4 * j]),
-                                        __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
-                                        __uint_as_float(v[4 * j + 3]));
+                        ptx::st_cg_v4(my_slot + ((c0 / 4 + j) * kBM + row_in_tile) * 4,
+                                      make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                  __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
                 }
-                ptx::tc_fence_before();
-                ptx::mbar_arrive(bar_acc_empty + acc * 8);  // MMA warp may start the next tile now
+                release_acc();  // the MMA warp may start the next tile now
                 __threadfence();
                 ptx::named_bar_sync(1, 128);
+                const int w_first = unit_owner(tile * KT, n_workers, p.total_units);
+                int* counter = p.counters + w_first * CG + cta_rank;
                 if (epi_tid == 0) {
-                    const int done = atomicAdd(p.counters + slot, k1 - k0) + (k1 - k0);
+                    const int done = atomicAdd(counter, k1 - k0) + (k1 - k0);
                     *finisher_flag = (done == KT) ? 1u : 0u;
                 }
                 ptx::named_bar_sync(1, 128);
                 const bool finisher = (*finisher_flag != 0u);
-                ptx::named_bar_sync(1, 128);  // flag may be rewritten only after everyone read it
+                ptx::named_bar_sync(1, 128);  // the flag may be rewritten only after everyone read it
                 if (finisher) {
+                    // Every contributor has published and fenced before bumping the counter.  Sum the
+                    // partials in ascending worker order, whoever the finisher is.
                     __threadfence();
+                    const int w_last = unit_owner(tile * KT + KT - 1, n_workers, p.total_units);
+                    // 32 columns per step; the next contributor's eight 16-byte loads are issued
+                    // before the current one's are summed, so 16 loads per thread stay in flight.
+                    auto slot_of = [&](int w) -> const float* {
+                        const int wk0 = max(unit_boundary(w, n_workers, p.total_units), tile * KT) - tile * KT;
+                        return p.scratch + static_cast<long long>(partial_slot(w, wk0, CG, cta_rank)) * (kBM * BN) + row_in_tile * 4;
+                    };
+                    const int n_contrib = w_last - w_first + 1;
+                    const int n_steps = (BN / 32) * n_contrib;
+                    float4 buf[2][8];
+                    {
+                        const float* src = slot_of(w_first);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) buf[0][j] = ptx::ld_cg_v4(src + j * (kBM * 4));
+                    }
+                    float s[32];
 #pragma unroll 1
-                    for (int c0 = 0; c0 < BN; c0 += 8) {
-                        float* src = slot_base + ((c0 / 4) * kBM + row_in_tile) * 4;
-                        const float4 lo = ptx::ld_cg_v4(src);
-                        const float4 hi = ptx::ld_cg_v4(src + kBM * 4);
-                        ptx::st_cg_v4(src, make_float4(0.f, 0.f, 0.f, 0.f));  // leave the slot zeroed
-                        ptx::st_cg_v4(src + kBM * 4, make_float4(0.f, 0.f, 0.f, 0.f));
-                        if (row < p.M) {
-                            uint4 q;
-                            __half2 h;
-                            h = __floats2half2_rn(lo.x, lo.y); q.x = *reinterpret_cast<uint32_t*>(&h);
-                            h = __floats2half2_rn(lo.z, lo.w); q.y = *reinterpret_cast<uint32_t*>(&h);
-                            h = __floats2half2_rn(hi.x, hi.y); q.z = *reinterpret_cast<uint32_t*>(&h);
-                            h = __floats2half2_rn(hi.z, hi.w); q.w = *reinterpret_cast<uint32_t*>(&h);
-                            *reinterpret_cast<uint4*>(c_row + c0) = q;
+                    for (int step = 0; step < n_steps; step += 2) {
+#pragma unroll
+                        for (int half = 0; half < 2; ++half) {
+                            const int cur = step + half;
+                            if (cur < n_steps) {
+                                const int nxt = cur + 1;
+                                if (nxt < n_steps) {
+                                    const float* src = slot_of(w_first + nxt % n_contrib) + (nxt / n_contrib) * 8 * (kBM * 4);
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) buf[half ^ 1][j] = ptx::ld_cg_v4(src + j * (kBM * 4));
+                                }
+                                const bool first = (cur % n_contrib) == 0;
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    s[4 * j + 0] = (first ? 0.f : s[4 * j + 0]) + buf[half][j].x;
+                                    s[4 * j + 1] = (first ? 0.f : s[4 * j + 1]) + buf[half][j].y;
+                                    s[4 * j + 2] = (first ? 0.f : s[4 * j + 2]) + buf[half][j].z;
+                                    s[4 * j + 3] = (first ? 0.f : s[4 * j + 3]) + buf[half][j].w;
+                                }
+                                if ((cur % n_contrib) == n_contrib - 1 && row < p.M) {
+                                    const int c0 = (cur / n_contrib) * 32;
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(c_row + c0 + 8 * j) = pack8_fp16(&s[8 * j]);
+                                }
+                            }
                         }
                     }
-                    if (epi_tid == 0) p.counters[slot] = 0;
+                    if (epi_tid == 0) *counter = 0;
                 }
             }
+            NVFP4_TRACE_END(trace_wait2);
             ++acc_it;
             u += k1 - k0;
         }
+#ifdef NVFP4_TRACE
+        if (epi_tid == 0) {
+            p.trace[blockIdx.x * 8 + 4] = trace_wait;
+            p.trace[blockIdx.x * 8 + 5] = trace_wait2;
+            p.trace[blockIdx.x * 8 + 6] = clock64() - trace_t_start;
+        }
+#endif
         if constexpr (TMA_STORE) {
             if (lane == 0) ptx::bulk_wait_group<0>();  // staging must outlive the stores that read it
         }
@@ -386,9 +554,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
         }
         __syncthreads();
     }
+    if constexpr (CG == 2) {
+        // neither CTA may retire (or free TMEM) while the other can still issue pair-wide work
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+    }
     if (warp == 1) {
         ptx::tc_fence_after();
-        ptx::tmem_dealloc<1>(tmem_base, kTmemCols);
+        ptx::tmem_dealloc<CG>(tmem_base, kTmemCols);
+    }
+    if constexpr (CG == 2) {
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
     }
 }
 

@@ -6,6 +6,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -56,7 +57,9 @@ struct MapEntry {
     CUtensorMap map;
 };
 
-constexpr int kMaxGrid = 296;  // scratch slots: two per SM on a 148-SM part
+constexpr int kMaxCtas = 160;                                          // persistent CTAs (one per SM; a B200 has 148)
+constexpr size_t kSlotBytes = static_cast<size_t>(kBM) * 256 * sizeof(float);  // one 128 x 256 fp32 partial tile
+constexpr size_t kScratchBytes = kMaxCtas * 2 * kSlotBytes;             // head + tail slot per CTA
 
 struct DeviceCtx {
     int device = -1;
@@ -67,8 +70,12 @@ struct DeviceCtx {
     int* status_host = nullptr;
     int* status_dev = nullptr;
     size_t scratch_bytes = 0;
+#ifdef NVFP4_TRACE
+    unsigned long long* trace = nullptr;
+#endif
+    int max_pairs = -1;  // CTA pairs that can be co-resident (cluster occupancy), queried once
     std::vector<MapEntry> maps;
-    bool smem_attr_set[8] = {false, false, false, false, false, false, false, false};
+    bool smem_attr_set[16] = {};
 };
 
 std::mutex g_mutex;
@@ -107,13 +114,17 @@ int get_ctx(DeviceCtx** out) {
 int ensure_scratch(DeviceCtx* c) {
     std::lock_guard<std::mutex> lock(g_mutex);
     if (c->scratch) return NVFP4_OK;
-    const size_t bytes = static_cast<size_t>(kMaxGrid) * kBM * 256 * sizeof(float);
-    CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&c->scratch), bytes));
-    CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&c->counters), kMaxGrid * sizeof(int)));
-    CUDA_TRY(cudaMemset(c->scratch, 0, bytes));
-    CUDA_TRY(cudaMemset(c->counters, 0, kMaxGrid * sizeof(int)));
+    // Partial-tile slots need no initialisation (they are written before they are read); the
+    // per-tile counters must be zero between launches.
+    CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&c->scratch), kScratchBytes));
+    CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&c->counters), kMaxCtas * sizeof(int)));
+    CUDA_TRY(cudaMemset(c->counters, 0, kMaxCtas * sizeof(int)));
+#ifdef NVFP4_TRACE
+    CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&c->trace), kMaxCtas * 8 * sizeof(unsigned long long)));
+    CUDA_TRY(cudaMemset(c->trace, 0, kMaxCtas * 8 * sizeof(unsigned long long)));
+#endif
     CUDA_TRY(cudaDeviceSynchronize());
-    c->scratch_bytes = bytes + kMaxGrid * sizeof(int);
+    c->scratch_bytes = kScratchBytes + kMaxCtas * sizeof(int);
     return NVFP4_OK;
 }
 
@@ -160,22 +171,52 @@ MapKey make_key(const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t
 
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
-template <int BN, int STAGES, bool TMA_STORE>
-int launch_gemm(DeviceCtx* c, int variant, const GemmParams& params, int grid, cudaStream_t stream, const char* name) {
-    using S = GemmSmem<BN, STAGES, TMA_STORE>;
-    auto kernel = gemm_nvfp4_kernel<BN, STAGES, TMA_STORE>;
+template <int CG, int BN, int STAGES, bool TMA_STORE>
+int launch_gemm(DeviceCtx* c, int variant, GemmParams& params, int grid_request, cudaStream_t stream, const char* name) {
+    using S = GemmSmem<CG, BN, STAGES, TMA_STORE>;
+    auto kernel = gemm_nvfp4_kernel<CG, BN, STAGES, TMA_STORE>;
     if (!c->smem_attr_set[variant]) {
         CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamicBytes));
         c->smem_attr_set[variant] = true;
     }
-    kernel<<<grid, kGemmThreads, S::kDynamicBytes, stream>>>(params);
-    CUDA_TRY(cudaGetLastError());
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = S::kDynamicBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    int max_ctas = c->num_sms;
+    if (CG == 2) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (c->max_pairs < 0) {
+            // All workers must be co-resident for the work split to be balanced: ask how many
+            // CTA pairs the device can hold at once (an SM without a free neighbour stays idle).
+            cfg.gridDim = dim3(c->num_sms & ~1, 1, 1);
+            int n = 0;
+            CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
+            c->max_pairs = n > 0 ? n : 1;
+        }
+        max_ctas = 2 * c->max_pairs;
+    }
+    int grid = grid_request > 0 ? grid_request : max_ctas;
+    if (grid > max_ctas) grid = max_ctas;
+    if (grid > kMaxCtas) grid = kMaxCtas;
+    grid = (grid / CG) * CG;
+    if (grid / CG > params.total_units) grid = params.total_units * CG;
+    if (grid < CG) grid = CG;
+    cfg.gridDim = dim3(grid, 1, 1);
+    CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, params));
     g_launches.fetch_add(1);
     t_last_kernel = name;
     return NVFP4_OK;
 }
 
-__global__ void bounded_wait_selftest_kernel(int* status, unsigned long long timeout_ns) {
+__global__ void bounded_wait_selftest_kernel(int* status, unsigned long long timeout_cycles) {
     __shared__ uint64_t bar;
     __shared__ uint32_t abort_flag;
     if (threadIdx.x == 0) {
@@ -183,7 +224,7 @@ __global__ void bounded_wait_selftest_kernel(int* status, unsigned long long tim
         abort_flag = 0;
         ptx::fence_mbar_init();
         // Nothing ever arrives on this barrier: the wait has to give up by itself.
-        const bool ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar), 0u, &abort_flag, timeout_ns);
+        const bool ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar), 0u, &abort_flag, timeout_cycles);
         if (!ok) {
             *reinterpret_cast<volatile int*>(status) = kStatusWaitTimeout;
             __threadfence_system();
@@ -224,8 +265,7 @@ int nvfp4_gemm(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* strea
     if (cf.tile_n != 0 && cf.tile_n != 128 && cf.tile_n != 256)
         return fail(NVFP4_ERR_INVALID_ARGUMENT, "tile_n must be 0, 128 or 256");
     if (cf.epilogue < 0 || cf.epilogue > 2) return fail(NVFP4_ERR_INVALID_ARGUMENT, "epilogue must be 0, 1 or 2");
-    if (cf.cta_group != 0 && cf.cta_group != 1)
-        return fail(NVFP4_ERR_UNSUPPORTED, "cta_group %d is not built", cf.cta_group);
+    if (cf.cta_group < 0 || cf.cta_group > 2) return fail(NVFP4_ERR_INVALID_ARGUMENT, "cta_group must be 0, 1 or 2");
 
     DeviceCtx* c = nullptr;
     if (int rc = get_ctx(&c)) return rc;
@@ -233,6 +273,10 @@ int nvfp4_gemm(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* strea
     if (int rc = ensure_scratch(c)) return rc;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
+    // A CTA pair (256-row tile, B shared through the pair) pays off as soon as there is more than
+    // one 128-row block; decode shapes (m <= 128) stay on single CTAs.
+    int cg = cf.cta_group;
+    if (cg == 0) cg = (p->m > kBM && p->n % 256 == 0) ? 2 : 1;
     int bn = cf.tile_n;
     if (bn == 0) bn = (p->n % 256 == 0) ? 256 : 128;
     if (p->n % bn) return fail(NVFP4_ERR_INVALID_ARGUMENT, "n = %d is not a multiple of tile_n = %d", p->n, bn);
@@ -240,7 +284,7 @@ int nvfp4_gemm(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* strea
     GemmParams g;
     std::memset(&g, 0, sizeof(g));
     g.M = p->m; g.N = p->n; g.K = p->k; g.L = p->l;
-    g.tiles_m = (p->m + kBM - 1) / kBM;
+    g.tiles_m = (p->m + kBM * cg - 1) / (kBM * cg);
     g.tiles_n = p->n / bn;
     g.k_tiles = p->k / kKPerStage;
     const long long units = static_cast<long long>(g.tiles_m) * g.tiles_n * p->l * g.k_tiles;
@@ -256,17 +300,17 @@ int nvfp4_gemm(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* strea
     g.sfb_batch_stride = p->sfb_perm_batch_stride;
     g.c_row_stride = p->c_row_stride;
     g.c_batch_stride = p->c_batch_stride;
-    g.timeout_ns = g_timeout_ns.load();
+    g.timeout_cycles = g_timeout_ns.load() * 2;  // SM clock <= 2 GHz: at least the requested time
+#ifdef NVFP4_TRACE
+    g.trace = c->trace;
+    g.dbg_flags = std::getenv("NVFP4_DBG_FLAGS") ? std::atoi(std::getenv("NVFP4_DBG_FLAGS")) : 0;
+#endif
 
-    int grid = cf.grid > 0 ? cf.grid : c->num_sms;
-    if (grid > kMaxGrid) grid = kMaxGrid;
-    if (grid > g.total_units) grid = g.total_units;
-
-    // TMA-store epilogue when whole tiles dominate (at least two tiles per CTA); otherwise the
+    // TMA-store epilogue when whole tiles dominate (at least two tiles per worker); otherwise the
     // deeper ring of the direct-store variant matters more than the store path.
     int epilogue = cf.epilogue;
     const long long tiles = static_cast<long long>(g.tiles_m) * g.tiles_n * p->l;
-    if (epilogue == 0) epilogue = (tiles >= 2LL * grid) ? 2 : 1;
+    if (epilogue == 0) epilogue = (tiles * cg >= 2LL * c->num_sms) ? 2 : 1;
 
     const uint64_t kbytes = static_cast<uint64_t>(p->k) / 2;
     const uint64_t a_bs = p->l > 1 ? static_cast<uint64_t>(p->a_batch_stride) : static_cast<uint64_t>(p->a_row_stride) * p->m;
@@ -274,7 +318,7 @@ int nvfp4_gemm(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* strea
     const uint64_t c_bs = p->l > 1 ? static_cast<uint64_t>(p->c_batch_stride) * 2 : static_cast<uint64_t>(p->c_row_stride) * 2 * p->m;
     if (int rc = get_map(c, make_key(p->a, kbytes, p->m, p->l, p->a_row_stride, a_bs, kBKBytes, kBM, CU_TENSOR_MAP_DATA_TYPE_UINT8),
                          CU_TENSOR_MAP_SWIZZLE_128B, &g.tma_a)) return rc;
-    if (int rc = get_map(c, make_key(p->b, kbytes, p->n, p->l, p->b_row_stride, b_bs, kBKBytes, bn, CU_TENSOR_MAP_DATA_TYPE_UINT8),
+    if (int rc = get_map(c, make_key(p->b, kbytes, p->n, p->l, p->b_row_stride, b_bs, kBKBytes, bn / cg, CU_TENSOR_MAP_DATA_TYPE_UINT8),
                          CU_TENSOR_MAP_SWIZZLE_128B, &g.tma_b)) return rc;
     if (epilogue == 2) {
         if (int rc = get_map(c, make_key(p->c, p->n, p->m, p->l, static_cast<uint64_t>(p->c_row_stride) * 2, c_bs, 64, 32,
@@ -282,10 +326,17 @@ int nvfp4_gemm(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* strea
                              CU_TENSOR_MAP_SWIZZLE_128B, &g.tma_c)) return rc;
     }
 
-    if (bn == 128 && epilogue == 2) return launch_gemm<128, 5, true>(c, 0, g, grid, stream, "gemm_1cta_n128_s5_tmastore");
-    if (bn == 128) return launch_gemm<128, 6, false>(c, 1, g, grid, stream, "gemm_1cta_n128_s6_direct");
-    if (epilogue == 2) return launch_gemm<256, 3, true>(c, 2, g, grid, stream, "gemm_1cta_n256_s3_tmastore");
-    return launch_gemm<256, 4, false>(c, 3, g, grid, stream, "gemm_1cta_n256_s4_direct");
+    const int grid = cf.grid;
+    if (cg == 2) {
+        if (bn == 256 && epilogue == 2) return launch_gemm<2, 256, 5, true>(c, 4, g, grid, stream, "gemm_2cta_n256_s5_tmastore");
+        if (bn == 256) return launch_gemm<2, 256, 5, false>(c, 5, g, grid, stream, "gemm_2cta_n256_s5_direct");
+        if (epilogue == 2) return launch_gemm<2, 128, 6, true>(c, 6, g, grid, stream, "gemm_2cta_n128_s6_tmastore");
+        return launch_gemm<2, 128, 7, false>(c, 7, g, grid, stream, "gemm_2cta_n128_s7_direct");
+    }
+    if (bn == 128 && epilogue == 2) return launch_gemm<1, 128, 5, true>(c, 0, g, grid, stream, "gemm_1cta_n128_s5_tmastore");
+    if (bn == 128) return launch_gemm<1, 128, 6, false>(c, 1, g, grid, stream, "gemm_1cta_n128_s6_direct");
+    if (epilogue == 2) return launch_gemm<1, 256, 3, true>(c, 2, g, grid, stream, "gemm_1cta_n256_s3_tmastore");
+    return launch_gemm<1, 256, 4, false>(c, 3, g, grid, stream, "gemm_1cta_n256_s4_direct");
 }
 
 int nvfp4_gemv(const nvfp4_problem* p, void* stream_v) {
@@ -341,11 +392,10 @@ int nvfp4_check_status(void* stream_v) {
     const int st = *reinterpret_cast<volatile int*>(c->status_host);
     if (st == kStatusOk) return NVFP4_OK;
     *reinterpret_cast<volatile int*>(c->status_host) = 0;
-    // A kernel that gave up may have left partial sums behind: restore the all-zero invariant.
+    // A kernel that gave up may have left tile counters half-way: restore the all-zero invariant.
     if (c->scratch) {
         CUDA_TRY(cudaDeviceSynchronize());
-        CUDA_TRY(cudaMemset(c->scratch, 0, c->scratch_bytes - kMaxGrid * sizeof(int)));
-        CUDA_TRY(cudaMemset(c->counters, 0, kMaxGrid * sizeof(int)));
+        CUDA_TRY(cudaMemset(c->counters, 0, kMaxCtas * sizeof(int)));
         CUDA_TRY(cudaDeviceSynchronize());
     }
     return fail(NVFP4_ERR_DEVICE_TIMEOUT, "a kernel gave up on a bounded wait (device status %d)", st);
@@ -357,7 +407,7 @@ int nvfp4_selftest_bounded_wait(void* stream_v) {
     DeviceCtx* c = nullptr;
     if (int rc = get_ctx(&c)) return rc;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>(c->status_dev, g_timeout_ns.load());
+    bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>(c->status_dev, g_timeout_ns.load() * 2);
     CUDA_TRY(cudaGetLastError());
     g_launches.fetch_add(1);
     return nvfp4_check_status(stream_v);
@@ -375,9 +425,20 @@ int nvfp4_plan_units(int total_units, int grid, int cta, int* begin, int* end, i
         return fail(NVFP4_ERR_INVALID_ARGUMENT, "bad partition query");
     *begin = unit_boundary(cta, grid, total_units);
     *end = unit_boundary(cta + 1, grid, total_units);
-    if (first_tile_slot) *first_tile_slot = unit_owner((*begin / k_tiles) * k_tiles, grid, total_units);
+    if (first_tile_slot) *first_tile_slot = partial_slot(cta, *begin % k_tiles, 1, 0);
     return NVFP4_OK;
 }
+
+#ifdef NVFP4_TRACE
+int nvfp4_debug_read_trace(unsigned long long* out, int n_ctas) {
+    DeviceCtx* c = nullptr;
+    if (int rc = get_ctx(&c)) return rc;
+    if (!c->trace || n_ctas > kMaxCtas) return fail(NVFP4_ERR_INVALID_ARGUMENT, "no trace buffer");
+    CUDA_TRY(cudaDeviceSynchronize());
+    CUDA_TRY(cudaMemcpy(out, c->trace, static_cast<size_t>(n_ctas) * 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    return NVFP4_OK;
+}
+#endif
 
 uint64_t nvfp4_launch_count(void) { return g_launches.load(); }
 
@@ -394,6 +455,9 @@ void nvfp4_shutdown(void) {
         cudaDeviceSynchronize();
         if (c->scratch) cudaFree(c->scratch);
         if (c->counters) cudaFree(c->counters);
+#ifdef NVFP4_TRACE
+        if (c->trace) cudaFree(c->trace);
+#endif
         if (c->status_host) cudaFreeHost(c->status_host);
         delete c;
         g_ctx[d] = nullptr;

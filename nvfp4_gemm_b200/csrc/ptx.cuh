@@ -20,6 +20,17 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
     return t;
 }
 
+// One lane of a fully converged warp, chosen by the hardware.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 // ----------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -56,26 +67,34 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
+#ifdef NVFP4_PLAIN_WAIT
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#else
         "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+#endif
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
 
-// Bounded wait.  Returns false when the limit ran out or another thread of the CTA
-// (or, through the same flag, of the CTA pair) already gave up.
+// Bounded wait.  Returns false when the limit ran out or another thread of the CTA already
+// gave up.  The limit is in SM clock cycles and is only consulted every 256 failed polls, so
+// the common case (the barrier completes within a few polls) costs nothing but the polls.
 template <bool kCluster = false>
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                                  uint64_t timeout_ns) {
+                                                  uint64_t timeout_cycles) {
     auto test = [&]() { return kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity); };
     if (test()) return true;
-    const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
+    long long t0 = 0;
     for (;;) {
         if (test()) return true;
-        if (((++spins) & 0x3Fu) == 0) {
+        if (((++spins) & 0xFFu) == 0) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > timeout_ns) {
+            const long long now = clock64();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (static_cast<uint64_t>(now - t0) > timeout_cycles) {
                 *abort_flag = 1u;
                 return false;
             }

@@ -123,4 +123,4 @@ def test_prefill_shape_full_size_sampled(sub, oracle):
     bq = oracle.dequantize(b[cols[:64], :, 0], sfb[cols[:64], :, 0]).astype(np.float64)
     want = bq @ aq
     have = out[:, torch.from_numpy(cols[:64]).cuda(), 0].double().sum(dim=0).cpu().numpy()
-    np.testing.assert_allclose(have, want, rtol=2e-3, atol=64.0)   # fp16 rounding of 4096 addends per column
+    np.testing.assert_allclose(have, want, rtol=2e-3, atol=2000.0)  # 4096 fp16-rounded addends of magnitude ~1e4 per column
