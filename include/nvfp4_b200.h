@@ -61,6 +61,7 @@ typedef struct nvfp4_gemm_config {
     int32_t epilogue;  /* 0 auto, 1 = 16-byte global stores, 2 = TMA store */
     int32_t grid;      /* 0 auto (one CTA per SM), else number of persistent CTAs */
     int32_t cta_group; /* 0 auto, 1 = one CTA per tile, 2 = CTA pair per 256-row tile */
+    int32_t split_k;   /* 0 auto, 1 = persistent stream-K kernel, 2 or 4 = cluster split-K (reduce in DSMEM) */
 } nvfp4_gemm_config;
 
 /*

@@ -46,7 +46,8 @@ class Problem(ctypes.Structure):
 
 class GemmConfig(ctypes.Structure):
     """Mirror of ``struct nvfp4_gemm_config``."""
-    _fields_ = [("tile_n", c_int32), ("epilogue", c_int32), ("grid", c_int32), ("cta_group", c_int32)]
+    _fields_ = [("tile_n", c_int32), ("epilogue", c_int32), ("grid", c_int32), ("cta_group", c_int32),
+                ("split_k", c_int32)]
 
 
 _lib = None

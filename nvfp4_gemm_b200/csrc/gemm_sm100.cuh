@@ -16,13 +16,14 @@
 //               permuted layout into a STAGES-deep shared-memory ring (full/empty mbarriers)
 //   warp 1      TMEM owner.  Leader CTA: MMA issuer -- tcgen05.cp scale atoms -> TMEM, four
 //               tcgen05.mma.kind::mxf4nvf4.block_scale (K = 64 each) per stage, tcgen05.commit
-//               to release the stage / publish the accumulator.  Second CTA of a pair: relays
-//               "my stage landed" to the leader's peer_full barriers.
+//               to release the stage / publish the accumulator.  In a pair both CTAs' loads
+//               signal the leader's full barrier (cp.async.bulk.tensor .cta_group::2).
 //   warps 2..5  epilogue: tcgen05.ld -> fp16 -> TMA store (or 16-byte stores), or the fp32
 //               partial-tile path
 //
 // No load in this file uses cluster multicast; the only cluster-wide signals are mbarrier
-// arrivals (remote arrive, tcgen05.commit to both CTAs of a pair).
+// arrivals (remote arrive, TMA completion on the leader's barrier, tcgen05.commit to both CTAs
+// of a pair).
 //
 // Replaces the reference's single-stage, fully serialised kernel (s_128t.py:375-466).
 #pragma once
@@ -49,17 +50,16 @@ struct GemmParams {
     CUtensorMap tma_a;   // {K/2 bytes, M rows, L}, box {128, 128, 1},    128B swizzle
     CUtensorMap tma_b;   // {K/2 bytes, N rows, L}, box {128, BN/CG, 1},  128B swizzle
     CUtensorMap tma_c;   // {N, M, L} fp16, box {64, 32, 1}, 128B swizzle (TMA-store epilogue)
-    const uint8_t* sfa;  // permuted scales of A
-    const uint8_t* sfb;  // permuted scales of B
+    CUtensorMap tma_sfa; // permuted scales of A as {128 words, K/64 atoms, row blocks, L}, box {128, 4, 1, 1}
+    CUtensorMap tma_sfb; // permuted scales of B, same view, box {128, 4, BN/128, 1}
     __half* c;
     float* scratch;      // partial-tile slots [worker][head|tail][cta of pair][BN/4][128][4] fp32
     int* counters;       // [worker][cta of pair] k-tiles published per shared tile; zero between launches
     int* status;         // host-visible status word
-    long long sfa_batch_stride, sfb_batch_stride;  // bytes
     long long c_row_stride, c_batch_stride;        // elements
     unsigned long long timeout_cycles;  // limit of every in-kernel wait, in SM clock cycles
 #ifdef NVFP4_TRACE
-    unsigned long long* trace;  // [grid][8] cycle counters (development builds only)
+    unsigned long long* trace;  // [grid][16] cycle counters (development builds only)
     int dbg_flags;              // 1: skip scale copies, 2: skip MMA and copies, 4: skip scale loads
 #endif
     int M, N, K, L;
@@ -67,7 +67,9 @@ struct GemmParams {
     int total_units;                // tiles_m * tiles_n * L * k_tiles
 };
 
-template <int CG, int BN, int STAGES, bool TMA_STORE>
+constexpr uint32_t kFixChunkBytes = kBM * 32 * 4;  // 32 fp32 columns of a partial tile
+
+template <int CG, int BN, int STAGES, bool TMA_STORE, int EPI_KB, int KS = 1>
 struct GemmSmem {
     static constexpr uint32_t kBRows = BN / CG;
     static constexpr uint32_t kABytes = kBM * kBKBytes;
@@ -75,15 +77,23 @@ struct GemmSmem {
     static constexpr uint32_t kSfaBytes = kMmaPerStage * kSfAtomBytes;
     static constexpr uint32_t kSfbBytes = (BN / 128) * kMmaPerStage * kSfAtomBytes;
     static constexpr uint32_t kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-    static constexpr uint32_t kStagingPerWarp = TMA_STORE ? 2 * 32 * 128 : 0;  // two 32-row x 128-byte buffers
-    static constexpr uint32_t kStagingOff = STAGES * kStageBytes;
-    static constexpr uint32_t kBarOff = kStagingOff + 4 * kStagingPerWarp;
+    // Epilogue scratch: TMA-store staging (two 32-row x 128-byte buffers per warp) and the
+    // landing buffers of the partial-tile reduction share it; they are never live together.
+    static constexpr uint32_t kEpiBytes = EPI_KB * 1024;
+    static constexpr uint32_t kStagingPerWarp = 2 * 32 * 128;
+    static constexpr uint32_t kFixBufs = kEpiBytes / kFixChunkBytes;
+    static constexpr uint32_t kEpiOff = STAGES * kStageBytes;
+    static constexpr uint32_t kBarOff = kEpiOff + kEpiBytes;
     static constexpr uint32_t kNumAcc = (BN <= 128) ? 2 : 1;
-    // full[STAGES] empty[STAGES] peer_full[STAGES] acc_full[2] acc_empty[2] | tmem slot | abort | finisher
-    static constexpr uint32_t kNumBars = 3 * STAGES + 4;
+    // full[STAGES] empty[STAGES] acc_full[2] acc_empty[2] fix_full[kFixBufs] | tmem slot | abort | finisher
+    static constexpr uint32_t kNumBars = 2 * STAGES + 4 + kFixBufs;
     static constexpr uint32_t kBytes = kBarOff + kNumBars * 8 + 16;
     static constexpr uint32_t kDynamicBytes = kBytes + 1024;  // slack for manual 1024-byte alignment
     static_assert(kStageBytes % 1024 == 0, "stage tiles must keep 1024-byte alignment");
+    static_assert(!TMA_STORE || kEpiBytes >= 4 * kStagingPerWarp, "TMA-store staging does not fit");
+    static_assert(kFixBufs >= 2, "the partial-tile reduction needs at least two landing buffers");
+    static_assert(KS == 1 || (CG == 1 && BN / KS >= 32 && kEpiBytes >= kBM * BN * 4),
+                  "cluster split-K: single-CTA MMAs, at least 32 columns per CTA, landing room for one fp32 tile");
     static_assert(kDynamicBytes <= 232448, "exceeds the 227 KB of shared memory one CTA may use");
 };
 
@@ -121,9 +131,9 @@ __device__ __forceinline__ uint4 pack8_fp16(const uint32_t* v) {
     return pack8_fp16(f);
 }
 
-template <int CG, int BN, int STAGES, bool TMA_STORE>
+template <int CG, int BN, int STAGES, bool TMA_STORE, int EPI_KB, int KS = 1>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __grid_constant__ GemmParams p) {
-    using S = GemmSmem<CG, BN, STAGES, TMA_STORE>;
+    using S = GemmSmem<CG, BN, STAGES, TMA_STORE, EPI_KB, KS>;
     constexpr int kNumAcc = S::kNumAcc;
     constexpr int kSfbColsPerMma = BN / 32;  // 4 TMEM columns per 128 rows of B
     constexpr int kBRows = S::kBRows;
@@ -134,10 +144,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
 
     const uint32_t bar_full = smem_base + S::kBarOff;
     const uint32_t bar_empty = bar_full + STAGES * 8;
-    const uint32_t bar_peer_full = bar_empty + STAGES * 8;
-    const uint32_t bar_acc_full = bar_peer_full + STAGES * 8;
+    const uint32_t bar_acc_full = bar_empty + STAGES * 8;
     const uint32_t bar_acc_empty = bar_acc_full + 2 * 8;
-    const uint32_t tmem_slot = bar_acc_empty + 2 * 8;
+    const uint32_t bar_fix_full = bar_acc_empty + 2 * 8;
+    const uint32_t tmem_slot = bar_fix_full + S::kFixBufs * 8;
     volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + S::kBarOff + S::kNumBars * 8);
     volatile uint32_t* abort_flag = tmem_slot_gen + 1;
     volatile uint32_t* finisher_flag = tmem_slot_gen + 2;
@@ -146,13 +156,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
     const int lane = threadIdx.x & 31;
     const int cta_rank = (CG == 2) ? static_cast<int>(ptx::cluster_ctarank()) : 0;
     const bool leader = (cta_rank == 0);
+    // Cluster split-K (KS > 1): the KS CTAs of a cluster share one output tile, each contracting
+    // 1/KS of K with its own MMAs and TMEM; the partial sums are exchanged through distributed
+    // shared memory and every CTA finalises BN/KS columns.
+    const int ks_rank = (KS > 1) ? static_cast<int>(ptx::cluster_ctarank()) : 0;
+    const uint32_t bar_land = bar_fix_full;  // KS > 1: "all peers' partial columns have landed"
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             ptx::mbar_init(bar_full + s * 8, 1);
             ptx::mbar_init(bar_empty + s * 8, 1);
-            ptx::mbar_init(bar_peer_full + s * 8, 1);
         }
+        for (uint32_t b = 0; b < S::kFixBufs; ++b) ptx::mbar_init(bar_fix_full + b * 8, (KS > 1 && b == 0) ? 128 * (KS - 1) : 1);
         for (int a = 0; a < 2; ++a) {
             ptx::mbar_init(bar_acc_full + a * 8, 1);
             ptx::mbar_init(bar_acc_empty + a * 8, 128 * CG);
@@ -162,10 +177,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&p.tma_a);
         ptx::prefetch_tensormap(&p.tma_b);
+        ptx::prefetch_tensormap(&p.tma_sfa);
+        ptx::prefetch_tensormap(&p.tma_sfb);
         if (TMA_STORE) ptx::prefetch_tensormap(&p.tma_c);
     }
-    if constexpr (CG == 2) {
-        // both CTAs of the pair are resident and have initialised their barriers before any
+    if constexpr (CG == 2 || KS > 1) {
+        // every CTA of the cluster is resident and has initialised its barriers before any
         // pair-wide instruction or remote arrival is issued
         __syncthreads();
         ptx::cluster_arrive();
@@ -180,12 +197,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_gen;
 
-    const int n_workers = gridDim.x / CG;
-    const int worker = blockIdx.x / CG;
-    const int u_begin = unit_boundary(worker, n_workers, p.total_units);
-    const int u_end = unit_boundary(worker + 1, n_workers, p.total_units);
     const int KT = p.k_tiles;
-    const int sf_kblocks = p.K / 64;  // scale atoms per 128-row block
+    const int n_workers = (KS > 1) ? static_cast<int>(gridDim.x) : static_cast<int>(gridDim.x) / CG;
+    const int worker = (KS > 1) ? static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x) / CG;
+    // stream-K: equal share of all units.  Cluster split-K: tile = cluster index, k-range by rank.
+    const int u_begin = (KS > 1) ? (worker / KS) * KT + (ks_rank * KT) / KS : unit_boundary(worker, n_workers, p.total_units);
+    const int u_end = (KS > 1) ? (worker / KS) * KT + ((ks_rank + 1) * KT) / KS : unit_boundary(worker + 1, n_workers, p.total_units);
     const uint64_t timeout = p.timeout_cycles;
 #ifdef NVFP4_TRACE
     const long long trace_t_start = clock64();
@@ -215,40 +232,36 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
             const int nb = tile % p.tiles_n;
             const int mb = ((tile / p.tiles_n) % p.tiles_m) * CG + cta_rank;  // 128-row block of this CTA
             const int l = tile / (p.tiles_n * p.tiles_m);
-            const uint8_t* sfa_tile = p.sfa + l * p.sfa_batch_stride + static_cast<long long>(mb) * sf_kblocks * kSfAtomBytes;
-            const uint8_t* sfb_tile = p.sfb + l * p.sfb_batch_stride +
-                                      static_cast<long long>(nb) * (BN / 128) * sf_kblocks * kSfAtomBytes;
             for (int kt = k0; kt < k1; ++kt) {
                 {
                     NVFP4_TRACE_BEGIN();
-                    ok = ptx::mbar_wait_bounded<CG == 2>(bar_empty + stage * 8, phase ^ 1u, abort_flag, timeout);
+                    ok = ptx::mbar_wait_bounded(bar_empty + stage * 8, phase ^ 1u, abort_flag, timeout);
                     ok = __all_sync(0xffffffffu, ok);
                     NVFP4_TRACE_END(trace_wait);
                 }
                 if (!ok) break;
                 if (ptx::elect_one()) {
-                    const uint32_t full = bar_full + stage * 8;
                     const uint32_t sa = smem_base + stage * S::kStageBytes;
                     const uint32_t sb = sa + S::kABytes;
                     const uint32_t ssfa = sb + S::kBBytes;
                     const uint32_t ssfb = ssfa + S::kSfaBytes;
-#ifdef NVFP4_TRACE
-                    if (p.dbg_flags & 4) {
-                        ptx::mbar_expect_tx(full, S::kABytes + S::kBBytes);
-                        ptx::tma_load_3d(sa, &p.tma_a, kt * kBKBytes, mb * kBM, l, full, pol_a);
-                        ptx::tma_load_3d(sb, &p.tma_b, kt * kBKBytes, nb * BN + cta_rank * kBRows, l, full, pol_b);
-                    } else
-#endif
-                    {
+                    if constexpr (CG == 1) {
+                        const uint32_t full = bar_full + stage * 8;
                         ptx::mbar_expect_tx(full, S::kStageBytes);
                         ptx::tma_load_3d(sa, &p.tma_a, kt * kBKBytes, mb * kBM, l, full, pol_a);
-                        ptx::tma_load_3d(sb, &p.tma_b, kt * kBKBytes, nb * BN + cta_rank * kBRows, l, full, pol_b);
-                        ptx::bulk_load(ssfa, sfa_tile + static_cast<long long>(kt) * S::kSfaBytes, S::kSfaBytes, full);
-#pragma unroll
-                        for (int h = 0; h < BN / 128; ++h)
-                            ptx::bulk_load(ssfb + h * S::kSfaBytes,
-                                           sfb_tile + (static_cast<long long>(h) * sf_kblocks + kt * kMmaPerStage) * kSfAtomBytes,
-                                           S::kSfaBytes, full);
+                        ptx::tma_load_3d(sb, &p.tma_b, kt * kBKBytes, nb * BN, l, full, pol_b);
+                        ptx::tma_load_4d(ssfa, &p.tma_sfa, 0, kt * kMmaPerStage, mb, l, full);
+                        ptx::tma_load_4d(ssfb, &p.tma_sfb, 0, kt * kMmaPerStage, nb * (BN / 128), l, full);
+                    } else {
+                        // Both CTAs of the pair report to the leader's barrier, which expects the
+                        // bytes of both stages (a completion may precede the expectation: the
+                        // transaction count is signed and the phase cannot end before the arrival).
+                        const uint32_t full = ptx::mapa_u32(bar_full + stage * 8, 0);
+                        if (leader) ptx::mbar_expect_tx(bar_full + stage * 8, 2 * S::kStageBytes);
+                        ptx::tma_load_3d_pair(sa, &p.tma_a, kt * kBKBytes, mb * kBM, l, full, pol_a);
+                        ptx::tma_load_3d_pair(sb, &p.tma_b, kt * kBKBytes, nb * BN + cta_rank * kBRows, l, full, pol_b);
+                        ptx::tma_load_4d_pair(ssfa, &p.tma_sfa, 0, kt * kMmaPerStage, mb, l, full);
+                        ptx::tma_load_4d_pair(ssfb, &p.tma_sfb, 0, kt * kMmaPerStage, nb * (BN / 128), l, full);
                     }
                 }
                 __syncwarp();
@@ -257,7 +270,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
             u += k1 - k0;
         }
 #ifdef NVFP4_TRACE
-        if (lane == 0) p.trace[blockIdx.x * 8 + 1] = trace_wait;
+        if (lane == 0) p.trace[blockIdx.x * 16 + 1] = trace_wait;
 #endif
     } else if (warp == 1) {
         if (leader) {
@@ -273,7 +286,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                 const uint32_t acc_phase = (acc_it / kNumAcc) & 1u;
                 {
                     NVFP4_TRACE_BEGIN();
-                    ok = ptx::mbar_wait_bounded<CG == 2>(bar_acc_empty + acc * 8, acc_phase ^ 1u, abort_flag, timeout);
+                    ok = ptx::mbar_wait_bounded(bar_acc_empty + acc * 8, acc_phase ^ 1u, abort_flag, timeout);
                     ok = __all_sync(0xffffffffu, ok);
                     NVFP4_TRACE_END(trace_wait2);
                 }
@@ -284,8 +297,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                     {
                         NVFP4_TRACE_BEGIN();
                         ok = ptx::mbar_wait_bounded(bar_full + stage * 8, phase, abort_flag, timeout);
-                        if constexpr (CG == 2)
-                            ok = ok && ptx::mbar_wait_bounded<true>(bar_peer_full + stage * 8, phase, abort_flag, timeout);
                         ok = __all_sync(0xffffffffu, ok);
                         NVFP4_TRACE_END(trace_wait);
                     }
@@ -353,24 +364,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
             }
 #ifdef NVFP4_TRACE
             if (lane == 0) {
-                p.trace[blockIdx.x * 8 + 2] = trace_wait;
-                p.trace[blockIdx.x * 8 + 3] = trace_wait2;
-                p.trace[blockIdx.x * 8 + 0] = clock64() - trace_t_start;
+                p.trace[blockIdx.x * 16 + 2] = trace_wait;
+                p.trace[blockIdx.x * 16 + 3] = trace_wait2;
+                p.trace[blockIdx.x * 16 + 0] = clock64() - trace_t_start;
             }
 #endif
-        } else {
-            // ----------------------------------- second CTA of a pair: stage relay
-            uint32_t stage = 0, phase = 0;
-            const int n_stages_total = u_end - u_begin;
-            for (int i = 0; i < n_stages_total; ++i) {
-                bool ok = ptx::mbar_wait_bounded(bar_full + stage * 8, phase, abort_flag, timeout);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                if (lane == 0) ptx::mbar_arrive_cluster(bar_peer_full + stage * 8, 0);
-                __syncwarp();
-                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-            }
         }
+        // (the second CTA of a pair has nothing to issue: the leader's instructions drive both)
     } else {
         // ------------------------------------------------------------ epilogue
         const int quad = warp & 3;             // TMEM lane quadrant this warp may read
@@ -378,6 +378,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
         const int epi_tid = threadIdx.x - 64;  // 0..127
         uint32_t acc_it = 0;
         uint32_t store_buf = 0;
+        uint32_t fix_it = 0;  // landing-buffer uses so far (buffer index and barrier parity)
         for (int u = u_begin; u < u_end;) {
             const int tile = u / KT;
             const int k0 = u - tile * KT;
@@ -392,7 +393,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
             bool got_acc;
             {
                 NVFP4_TRACE_BEGIN();
-                got_acc = ptx::mbar_wait_bounded<CG == 2>(bar_acc_full + acc * 8, acc_phase, abort_flag, timeout);
+                got_acc = ptx::mbar_wait_bounded(bar_acc_full + acc * 8, acc_phase, abort_flag, timeout);
                 NVFP4_TRACE_END(trace_wait);
             }
             if (!ptx::named_bar_and(2, 128, got_acc)) break;
@@ -408,11 +409,65 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                 else ptx::mbar_arrive(bar_acc_empty + acc * 8);
             };
 
-            if (whole_tile) {
+            if constexpr (KS > 1) {
+                constexpr int kMyCols = BN / KS;                     // columns this CTA finalises
+                constexpr uint32_t kPieceBytes = kMyCols * kBM * 4;  // one sender's columns, [col/4][128 rows][4]
+                const uint32_t land = smem_base + S::kEpiOff;
+                const float* land_gen = reinterpret_cast<const float*>(smem_gen + S::kEpiOff);
+                // 1. send every peer the columns it finalises
+#pragma unroll 1
+                for (int q = 0; q < KS; ++q) {
+                    if (q == ks_rank) continue;
+                    const uint32_t dst = ptx::mapa_u32(land + ks_rank * kPieceBytes + row_in_tile * 16, q);
+#pragma unroll 1
+                    for (int c0 = 0; c0 < kMyCols; c0 += 32) {
+                        uint32_t v[32];
+                        ptx::tc_ld_32cols(t_acc + q * kMyCols + c0, v);
+                        ptx::tc_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            ptx::st_shared_cluster_v4(dst + (c0 / 4 + j) * (kBM * 16), v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    }
+                    ptx::mbar_arrive_cluster(bar_land, q);  // release: my stores above are visible to q
+                }
+                // 2. wait for the other CTAs' partial sums of my columns
+                const bool landed = ptx::mbar_wait_bounded<true>(bar_land, 0u, abort_flag, timeout);
+                if (!ptx::named_bar_and(2, 128, landed)) break;
+                // 3. sum in ascending rank order (my own term comes from TMEM) and store fp16
+#pragma unroll 1
+                for (int c0 = 0; c0 < kMyCols; c0 += 32) {
+                    uint32_t v[32];
+                    ptx::tc_ld_32cols(t_acc + ks_rank * kMyCols + c0, v);
+                    ptx::tc_wait_ld();
+                    float s[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) s[i] = 0.f;
+#pragma unroll 1
+                    for (int r = 0; r < KS; ++r) {
+                        if (r == ks_rank) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) s[i] += __uint_as_float(v[i]);
+                        } else {
+                            const float* src = land_gen + r * (kPieceBytes / 4) + (c0 / 4) * (kBM * 4) + row_in_tile * 4;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const float4 t = *reinterpret_cast<const float4*>(src + j * (kBM * 4));
+                                s[4 * j] += t.x; s[4 * j + 1] += t.y; s[4 * j + 2] += t.z; s[4 * j + 3] += t.w;
+                            }
+                        }
+                    }
+                    if (row < p.M) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            *reinterpret_cast<uint4*>(c_row + ks_rank * kMyCols + c0 + 8 * j) = pack8_fp16(&s[8 * j]);
+                    }
+                }
+                release_acc();
+            } else if (whole_tile) {
                 if constexpr (TMA_STORE) {
                     // 64 columns (128 bytes of fp16) at a time through a swizzled 32-row staging buffer.
-                    uint8_t* staging_gen = smem_gen + S::kStagingOff + (warp - 2) * S::kStagingPerWarp;
-                    const uint32_t staging = smem_base + S::kStagingOff + (warp - 2) * S::kStagingPerWarp;
+                    uint8_t* staging_gen = smem_gen + S::kEpiOff + (warp - 2) * S::kStagingPerWarp;
+                    const uint32_t staging = smem_base + S::kEpiOff + (warp - 2) * S::kStagingPerWarp;
 #pragma unroll 1
                     for (int c0 = 0; c0 < BN; c0 += 64) {
                         uint32_t v[2][32];
@@ -450,6 +505,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
             } else {
                 // Partial tile: publish this worker's k-range as fp32 in its own slot.  Slot layout
                 // [BN/4][128 rows][4] keeps every warp-wide 16-byte access contiguous (512 bytes).
+#ifdef NVFP4_TRACE
+#define NVFP4_MARK(i) if (epi_tid == 0) p.trace[blockIdx.x * 16 + (i)] = clock64() - trace_t_start
+#else
+#define NVFP4_MARK(i)
+#endif
+                NVFP4_MARK(8);
                 float* my_slot = p.scratch + static_cast<long long>(partial_slot(worker, k0, CG, cta_rank)) * (kBM * BN);
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -462,8 +523,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                                       make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
                                                   __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
                 }
+                NVFP4_MARK(9);
                 release_acc();  // the MMA warp may start the next tile now
                 __threadfence();
+                NVFP4_MARK(10);
                 ptx::named_bar_sync(1, 128);
                 const int w_first = unit_owner(tile * KT, n_workers, p.total_units);
                 int* counter = p.counters + w_first * CG + cta_rank;
@@ -474,54 +537,73 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                 ptx::named_bar_sync(1, 128);
                 const bool finisher = (*finisher_flag != 0u);
                 ptx::named_bar_sync(1, 128);  // the flag may be rewritten only after everyone read it
+                NVFP4_MARK(11);
                 if (finisher) {
                     // Every contributor has published and fenced before bumping the counter.  Sum the
                     // partials in ascending worker order, whoever the finisher is.
                     __threadfence();
                     const int w_last = unit_owner(tile * KT + KT - 1, n_workers, p.total_units);
-                    // 32 columns per step; the next contributor's eight 16-byte loads are issued
-                    // before the current one's are summed, so 16 loads per thread stay in flight.
-                    auto slot_of = [&](int w) -> const float* {
-                        const int wk0 = max(unit_boundary(w, n_workers, p.total_units), tile * KT) - tile * KT;
-                        return p.scratch + static_cast<long long>(partial_slot(w, wk0, CG, cta_rank)) * (kBM * BN) + row_in_tile * 4;
+                    // The partials are pulled into shared memory with bulk copies, kFixBufs chunks of
+                    // 32 columns (16 KB) in flight, and summed from there.
+                    if constexpr (TMA_STORE) {
+                        if (lane == 0) ptx::bulk_wait_group_read<0>();  // staging still read by earlier tile stores
+                    }
+                    ptx::named_bar_sync(1, 128);
+                    // The first contributor started the tile (its "tail" slot); every later one joined
+                    // it from inside (its "head" slot), so no partition arithmetic is needed here.
+                    auto chunk_src = [&](int step, int n_contrib) -> const float* {
+                        const int i = step % n_contrib;
+                        const int slot = ((w_first + i) * 2 + (i == 0 ? 1 : 0)) * CG + cta_rank;
+                        return p.scratch + static_cast<long long>(slot) * (kBM * BN) +
+                               static_cast<long long>(step / n_contrib) * (kFixChunkBytes / 4);
                     };
                     const int n_contrib = w_last - w_first + 1;
                     const int n_steps = (BN / 32) * n_contrib;
-                    float4 buf[2][8];
-                    {
-                        const float* src = slot_of(w_first);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) buf[0][j] = ptx::ld_cg_v4(src + j * (kBM * 4));
-                    }
-                    float s[32];
-#pragma unroll 1
-                    for (int step = 0; step < n_steps; step += 2) {
-#pragma unroll
-                        for (int half = 0; half < 2; ++half) {
-                            const int cur = step + half;
-                            if (cur < n_steps) {
-                                const int nxt = cur + 1;
-                                if (nxt < n_steps) {
-                                    const float* src = slot_of(w_first + nxt % n_contrib) + (nxt / n_contrib) * 8 * (kBM * 4);
-#pragma unroll
-                                    for (int j = 0; j < 8; ++j) buf[half ^ 1][j] = ptx::ld_cg_v4(src + j * (kBM * 4));
-                                }
-                                const bool first = (cur % n_contrib) == 0;
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) {
-                                    s[4 * j + 0] = (first ? 0.f : s[4 * j + 0]) + buf[half][j].x;
-                                    s[4 * j + 1] = (first ? 0.f : s[4 * j + 1]) + buf[half][j].y;
-                                    s[4 * j + 2] = (first ? 0.f : s[4 * j + 2]) + buf[half][j].z;
-                                    s[4 * j + 3] = (first ? 0.f : s[4 * j + 3]) + buf[half][j].w;
-                                }
-                                if ((cur % n_contrib) == n_contrib - 1 && row < p.M) {
-                                    const int c0 = (cur / n_contrib) * 32;
-#pragma unroll
-                                    for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(c_row + c0 + 8 * j) = pack8_fp16(&s[8 * j]);
-                                }
-                            }
+                    const uint32_t fix_smem = smem_base + S::kEpiOff;
+                    const float* fix_gen = reinterpret_cast<const float*>(smem_gen + S::kEpiOff);
+                    if (epi_tid == 0) {
+                        ptx::fence_proxy_async_all();  // other CTAs' plain stores -> this CTA's bulk reads
+                        for (int i = 0; i < static_cast<int>(S::kFixBufs) && i < n_steps; ++i) {
+                            const int bi = (fix_it + i) % S::kFixBufs;
+                            ptx::mbar_expect_tx(bar_fix_full + bi * 8, kFixChunkBytes);
+                            ptx::bulk_load(fix_smem + bi * kFixChunkBytes, chunk_src(i, n_contrib), kFixChunkBytes, bar_fix_full + bi * 8);
                         }
                     }
+                    NVFP4_MARK(12);
+                    float s[32];
+                    bool fix_ok = true;
+#pragma unroll 1
+                    for (int step = 0; step < n_steps; ++step) {
+                        const int b = (fix_it + step) % S::kFixBufs;
+                        const uint32_t par = ((fix_it + step) / S::kFixBufs) & 1u;
+                        fix_ok = ptx::mbar_wait_bounded(bar_fix_full + b * 8, par, abort_flag, timeout) && fix_ok;
+                        const float* src = fix_gen + b * (kFixChunkBytes / 4) + row_in_tile * 4;
+                        const bool first = (step % n_contrib) == 0;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float4 v = *reinterpret_cast<const float4*>(src + j * (kBM * 4));
+                            s[4 * j + 0] = (first ? 0.f : s[4 * j + 0]) + v.x;
+                            s[4 * j + 1] = (first ? 0.f : s[4 * j + 1]) + v.y;
+                            s[4 * j + 2] = (first ? 0.f : s[4 * j + 2]) + v.z;
+                            s[4 * j + 3] = (first ? 0.f : s[4 * j + 3]) + v.w;
+                        }
+                        if ((step % n_contrib) == n_contrib - 1 && row < p.M && fix_ok) {
+                            const int c0 = (step / n_contrib) * 32;
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(c_row + c0 + 8 * j) = pack8_fp16(&s[8 * j]);
+                        }
+                        ptx::named_bar_sync(1, 128);  // everyone is done with buffer b
+                        if (epi_tid == 0 && step + static_cast<int>(S::kFixBufs) < n_steps) {
+                            const int nxt = step + S::kFixBufs;
+                            ptx::mbar_expect_tx(bar_fix_full + b * 8, kFixChunkBytes);
+                            ptx::bulk_load(fix_smem + b * kFixChunkBytes, chunk_src(nxt, n_contrib), kFixChunkBytes, bar_fix_full + b * 8);
+                        }
+                    }
+                    fix_it += n_steps;
+                    NVFP4_MARK(13);
+#ifdef NVFP4_TRACE
+                    if (epi_tid == 0) p.trace[blockIdx.x * 16 + 14] = n_steps;
+#endif
                     if (epi_tid == 0) *counter = 0;
                 }
             }
@@ -531,9 +613,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
         }
 #ifdef NVFP4_TRACE
         if (epi_tid == 0) {
-            p.trace[blockIdx.x * 8 + 4] = trace_wait;
-            p.trace[blockIdx.x * 8 + 5] = trace_wait2;
-            p.trace[blockIdx.x * 8 + 6] = clock64() - trace_t_start;
+            p.trace[blockIdx.x * 16 + 4] = trace_wait;
+            p.trace[blockIdx.x * 16 + 5] = trace_wait2;
+            p.trace[blockIdx.x * 16 + 6] = clock64() - trace_t_start;
         }
 #endif
         if constexpr (TMA_STORE) {
@@ -554,8 +636,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
         }
         __syncthreads();
     }
-    if constexpr (CG == 2) {
-        // neither CTA may retire (or free TMEM) while the other can still issue pair-wide work
+    if constexpr (CG == 2 || KS > 1) {
+        // no CTA may retire (or free TMEM) while another can still issue pair-wide work or write
+        // into its shared memory
         ptx::cluster_arrive();
         ptx::cluster_wait();
     }

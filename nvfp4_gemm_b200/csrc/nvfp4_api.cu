@@ -46,10 +46,12 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
 
 struct MapKey {
     const void* ptr;
-    uint64_t dims[3];
-    uint64_t strides[2];
-    uint32_t box[3];
+    uint64_t dims[4];
+    uint64_t strides[3];
+    uint32_t box[4];
     int dtype;
+    int rank;
+    int swizzle;
     bool operator==(const MapKey& o) const { return std::memcmp(this, &o, sizeof(MapKey)) == 0; }
 };
 struct MapEntry {
@@ -120,8 +122,8 @@ int ensure_scratch(DeviceCtx* c) {
     CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&c->counters), kMaxCtas * sizeof(int)));
     CUDA_TRY(cudaMemset(c->counters, 0, kMaxCtas * sizeof(int)));
 #ifdef NVFP4_TRACE
-    CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&c->trace), kMaxCtas * 8 * sizeof(unsigned long long)));
-    CUDA_TRY(cudaMemset(c->trace, 0, kMaxCtas * 8 * sizeof(unsigned long long)));
+    CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&c->trace), kMaxCtas * 16 * sizeof(unsigned long long)));
+    CUDA_TRY(cudaMemset(c->trace, 0, kMaxCtas * 16 * sizeof(unsigned long long)));
 #endif
     CUDA_TRY(cudaDeviceSynchronize());
     c->scratch_bytes = kScratchBytes + kMaxCtas * sizeof(int);
@@ -130,7 +132,7 @@ int ensure_scratch(DeviceCtx* c) {
 
 // Tensor maps are cached by (pointer, extents, strides, box): re-encoding four maps per call,
 // as the reference does (s_128t.py:569-577), costs more than a short GEMM.
-int get_map(DeviceCtx* c, const MapKey& key, CUtensorMapSwizzle swizzle, CUtensorMap* out) {
+int get_map(DeviceCtx* c, const MapKey& key, CUtensorMap* out) {
     std::lock_guard<std::mutex> lock(g_mutex);
     for (const MapEntry& e : c->maps)
         if (e.key == key) {
@@ -140,23 +142,25 @@ int get_map(DeviceCtx* c, const MapKey& key, CUtensorMapSwizzle swizzle, CUtenso
     MapEntry e;
     std::memset(&e, 0, sizeof(e));
     e.key = key;
-    cuuint64_t dims[3] = {key.dims[0], key.dims[1], key.dims[2]};
-    cuuint64_t strides[2] = {key.strides[0], key.strides[1]};
-    cuuint32_t box[3] = {key.box[0], key.box[1], key.box[2]};
-    cuuint32_t elem[3] = {1, 1, 1};
-    CUresult r = g_encode(&e.map, static_cast<CUtensorMapDataType>(key.dtype), 3, const_cast<void*>(key.ptr), dims, strides,
-                          box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    cuuint64_t dims[4] = {key.dims[0], key.dims[1], key.dims[2], key.dims[3]};
+    cuuint64_t strides[3] = {key.strides[0], key.strides[1], key.strides[2]};
+    cuuint32_t box[4] = {key.box[0], key.box[1], key.box[2], key.box[3]};
+    cuuint32_t elem[4] = {1, 1, 1, 1};
+    CUresult r = g_encode(&e.map, static_cast<CUtensorMapDataType>(key.dtype), key.rank, const_cast<void*>(key.ptr), dims,
+                          strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, static_cast<CUtensorMapSwizzle>(key.swizzle),
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
-        return fail(NVFP4_ERR_CUDA, "cuTensorMapEncodeTiled failed (CUresult %d) dims {%llu,%llu,%llu} strides {%llu,%llu}",
-                    static_cast<int>(r), (unsigned long long)dims[0], (unsigned long long)dims[1],
-                    (unsigned long long)dims[2], (unsigned long long)strides[0], (unsigned long long)strides[1]);
+        return fail(NVFP4_ERR_CUDA, "cuTensorMapEncodeTiled failed (CUresult %d) rank %d dims {%llu,%llu,%llu,%llu} strides {%llu,%llu,%llu}",
+                    static_cast<int>(r), key.rank, (unsigned long long)dims[0], (unsigned long long)dims[1],
+                    (unsigned long long)dims[2], (unsigned long long)dims[3], (unsigned long long)strides[0],
+                    (unsigned long long)strides[1], (unsigned long long)strides[2]);
     if (c->maps.size() >= 256) c->maps.erase(c->maps.begin());
     c->maps.push_back(e);
     *out = e.map;
     return NVFP4_OK;
 }
 
+// Operand / output tiles: {inner extent, rows, batches}, 128-byte swizzle.
 MapKey make_key(const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s0, uint64_t s1, uint32_t b0, uint32_t b1,
                 int dtype) {
     MapKey k;
@@ -166,15 +170,36 @@ MapKey make_key(const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t
     k.strides[0] = s0; k.strides[1] = s1;
     k.box[0] = b0; k.box[1] = b1; k.box[2] = 1;
     k.dtype = dtype;
+    k.rank = 3;
+    k.swizzle = CU_TENSOR_MAP_SWIZZLE_128B;
     return k;
+}
+
+// Permuted scale factors: 512-byte atoms (128 words), K/64 atoms per 128-row block, un-swizzled
+// (tcgen05.cp reads them as 32 rows of 16 bytes).  Box = the four atoms of one 256-wide k-tile
+// for `blocks` consecutive row blocks.
+MapKey make_sf_key(const void* ptr, int rows, int k, int l, uint64_t batch_stride, uint32_t blocks) {
+    MapKey key;
+    std::memset(&key, 0, sizeof(key));
+    const uint64_t atoms_k = static_cast<uint64_t>(k) / 64;
+    const uint64_t row_blocks = (static_cast<uint64_t>(rows) + 127) / 128;
+    key.ptr = ptr;
+    key.dims[0] = kSfAtomBytes / 4; key.dims[1] = atoms_k; key.dims[2] = row_blocks; key.dims[3] = l;
+    key.strides[0] = kSfAtomBytes; key.strides[1] = atoms_k * kSfAtomBytes;
+    key.strides[2] = l > 1 ? batch_stride : row_blocks * atoms_k * kSfAtomBytes;
+    key.box[0] = kSfAtomBytes / 4; key.box[1] = kMmaPerStage; key.box[2] = blocks; key.box[3] = 1;
+    key.dtype = CU_TENSOR_MAP_DATA_TYPE_UINT32;
+    key.rank = 4;
+    key.swizzle = CU_TENSOR_MAP_SWIZZLE_NONE;
+    return key;
 }
 
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
-template <int CG, int BN, int STAGES, bool TMA_STORE>
+template <int CG, int BN, int STAGES, bool TMA_STORE, int EPI_KB>
 int launch_gemm(DeviceCtx* c, int variant, GemmParams& params, int grid_request, cudaStream_t stream, const char* name) {
-    using S = GemmSmem<CG, BN, STAGES, TMA_STORE>;
-    auto kernel = gemm_nvfp4_kernel<CG, BN, STAGES, TMA_STORE>;
+    using S = GemmSmem<CG, BN, STAGES, TMA_STORE, EPI_KB>;
+    auto kernel = gemm_nvfp4_kernel<CG, BN, STAGES, TMA_STORE, EPI_KB>;
     if (!c->smem_attr_set[variant]) {
         CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamicBytes));
         c->smem_attr_set[variant] = true;
@@ -206,10 +231,51 @@ int launch_gemm(DeviceCtx* c, int variant, GemmParams& params, int grid_request,
     int grid = grid_request > 0 ? grid_request : max_ctas;
     if (grid > max_ctas) grid = max_ctas;
     if (grid > kMaxCtas) grid = kMaxCtas;
-    grid = (grid / CG) * CG;
-    if (grid / CG > params.total_units) grid = params.total_units * CG;
-    if (grid < CG) grid = CG;
+    int workers = grid / CG;
+    if (grid_request <= 0) {
+        // Splitting a tile's K range between workers costs a round trip through global scratch,
+        // which only pays when every share keeps at least ~8 k-tiles; with fewer tiles than
+        // workers and a short K, run one whole tile per worker instead.
+        const int tiles = params.total_units / params.k_tiles;
+        if (tiles < workers) {
+            int w = params.total_units / 8;
+            if (w < tiles) w = tiles;
+            if (w < workers) workers = w;
+        }
+    }
+    if (workers > params.total_units) workers = params.total_units;
+    if (workers < 1) workers = 1;
+    grid = workers * CG;
     cfg.gridDim = dim3(grid, 1, 1);
+    CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, params));
+    g_launches.fetch_add(1);
+    t_last_kernel = name;
+    return NVFP4_OK;
+}
+
+// Cluster split-K launch: one cluster of KS CTAs per 128 x BN output tile.
+template <int BN, int STAGES, int EPI_KB, int KS>
+int launch_gemm_splitk(DeviceCtx* c, int variant, GemmParams& params, cudaStream_t stream, const char* name) {
+    using S = GemmSmem<1, BN, STAGES, false, EPI_KB, KS>;
+    auto kernel = gemm_nvfp4_kernel<1, BN, STAGES, false, EPI_KB, KS>;
+    if (!c->smem_attr_set[variant]) {
+        CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamicBytes));
+        c->smem_attr_set[variant] = true;
+    }
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = S::kDynamicBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = KS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const int tiles = params.total_units / params.k_tiles;
+    cfg.gridDim = dim3(tiles * KS, 1, 1);
     CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, params));
     g_launches.fetch_add(1);
     t_last_kernel = name;
@@ -260,12 +326,14 @@ int nvfp4_gemm(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* strea
                      p->sfa_perm_batch_stride % 16 || p->sfb_perm_batch_stride % 16))
         return fail(NVFP4_ERR_INVALID_ARGUMENT, "batch strides must keep 16-byte alignment");
 
-    nvfp4_gemm_config cf = {0, 0, 0, 0};
+    nvfp4_gemm_config cf = {0, 0, 0, 0, 0};
     if (cfg) cf = *cfg;
     if (cf.tile_n != 0 && cf.tile_n != 128 && cf.tile_n != 256)
         return fail(NVFP4_ERR_INVALID_ARGUMENT, "tile_n must be 0, 128 or 256");
     if (cf.epilogue < 0 || cf.epilogue > 2) return fail(NVFP4_ERR_INVALID_ARGUMENT, "epilogue must be 0, 1 or 2");
     if (cf.cta_group < 0 || cf.cta_group > 2) return fail(NVFP4_ERR_INVALID_ARGUMENT, "cta_group must be 0, 1 or 2");
+    if (cf.split_k != 0 && cf.split_k != 1 && cf.split_k != 2 && cf.split_k != 4)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "split_k must be 0, 1, 2 or 4");
 
     DeviceCtx* c = nullptr;
     if (int rc = get_ctx(&c)) return rc;
@@ -290,14 +358,10 @@ int nvfp4_gemm(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* strea
     const long long units = static_cast<long long>(g.tiles_m) * g.tiles_n * p->l * g.k_tiles;
     if (units > 0x7fffffffLL) return fail(NVFP4_ERR_INVALID_ARGUMENT, "problem too large: %lld work units", units);
     g.total_units = static_cast<int>(units);
-    g.sfa = static_cast<const uint8_t*>(p->sfa_perm);
-    g.sfb = static_cast<const uint8_t*>(p->sfb_perm);
     g.c = static_cast<__half*>(p->c);
     g.scratch = c->scratch;
     g.counters = c->counters;
     g.status = c->status_dev;
-    g.sfa_batch_stride = p->sfa_perm_batch_stride;
-    g.sfb_batch_stride = p->sfb_perm_batch_stride;
     g.c_row_stride = p->c_row_stride;
     g.c_batch_stride = p->c_batch_stride;
     g.timeout_cycles = g_timeout_ns.load() * 2;  // SM clock <= 2 GHz: at least the requested time
@@ -317,26 +381,55 @@ int nvfp4_gemm(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* strea
     const uint64_t b_bs = p->l > 1 ? static_cast<uint64_t>(p->b_batch_stride) : static_cast<uint64_t>(p->b_row_stride) * p->n;
     const uint64_t c_bs = p->l > 1 ? static_cast<uint64_t>(p->c_batch_stride) * 2 : static_cast<uint64_t>(p->c_row_stride) * 2 * p->m;
     if (int rc = get_map(c, make_key(p->a, kbytes, p->m, p->l, p->a_row_stride, a_bs, kBKBytes, kBM, CU_TENSOR_MAP_DATA_TYPE_UINT8),
-                         CU_TENSOR_MAP_SWIZZLE_128B, &g.tma_a)) return rc;
+                         &g.tma_a)) return rc;
     if (int rc = get_map(c, make_key(p->b, kbytes, p->n, p->l, p->b_row_stride, b_bs, kBKBytes, bn / cg, CU_TENSOR_MAP_DATA_TYPE_UINT8),
-                         CU_TENSOR_MAP_SWIZZLE_128B, &g.tma_b)) return rc;
+                         &g.tma_b)) return rc;
+    if (int rc = get_map(c, make_sf_key(p->sfa_perm, p->m, p->k, p->l, p->sfa_perm_batch_stride, 1), &g.tma_sfa)) return rc;
+    if (int rc = get_map(c, make_sf_key(p->sfb_perm, p->n, p->k, p->l, p->sfb_perm_batch_stride, bn / 128), &g.tma_sfb)) return rc;
     if (epilogue == 2) {
         if (int rc = get_map(c, make_key(p->c, p->n, p->m, p->l, static_cast<uint64_t>(p->c_row_stride) * 2, c_bs, 64, 32,
                                          CU_TENSOR_MAP_DATA_TYPE_FLOAT16),
-                             CU_TENSOR_MAP_SWIZZLE_128B, &g.tma_c)) return rc;
+                             &g.tma_c)) return rc;
+    }
+
+    // Decode shapes (one 128-row block, fewer tiles than half the SMs): split K across a cluster
+    // and reduce through distributed shared memory instead of through global scratch.
+    int ks = cf.split_k;
+    if (ks == 0) {
+        ks = 1;
+        const long long tiles128 = static_cast<long long>(p->n / 128) * p->l;
+        if (p->m <= kBM && cf.cta_group != 2 && (cf.tile_n == 0 || cf.tile_n == 128) && cf.grid == 0) {
+            if (tiles128 * 4 <= c->num_sms && g.k_tiles >= 8) ks = 4;
+            else if (tiles128 * 2 <= c->num_sms && g.k_tiles >= 4) ks = 2;
+        }
+    }
+    if (ks > 1) {
+        if (cf.cta_group == 2) return fail(NVFP4_ERR_INVALID_ARGUMENT, "split_k > 1 uses single-CTA tiles (cta_group 1)");
+        if (bn != 128 && cf.tile_n != 0) return fail(NVFP4_ERR_INVALID_ARGUMENT, "split_k > 1 needs tile_n 128");
+        if (g.k_tiles < ks) return fail(NVFP4_ERR_INVALID_ARGUMENT, "split_k = %d needs k >= %d", ks, ks * kKPerStage);
+        // plan for single-CTA 128 x 128 tiles, whatever the stream-K planning above chose
+        bn = 128;
+        g.tiles_m = (p->m + kBM - 1) / kBM;
+        g.tiles_n = p->n / bn;
+        g.total_units = g.tiles_m * g.tiles_n * p->l * g.k_tiles;
+        if (int rc = get_map(c, make_key(p->b, kbytes, p->n, p->l, p->b_row_stride, b_bs, kBKBytes, bn, CU_TENSOR_MAP_DATA_TYPE_UINT8),
+                             &g.tma_b)) return rc;
+        if (int rc = get_map(c, make_sf_key(p->sfb_perm, p->n, p->k, p->l, p->sfb_perm_batch_stride, 1), &g.tma_sfb)) return rc;
+        if (ks == 2) return launch_gemm_splitk<128, 4, 64, 2>(c, 8, g, stream, "gemm_splitk2_n128_s4");
+        return launch_gemm_splitk<128, 4, 64, 4>(c, 9, g, stream, "gemm_splitk4_n128_s4");
     }
 
     const int grid = cf.grid;
     if (cg == 2) {
-        if (bn == 256 && epilogue == 2) return launch_gemm<2, 256, 5, true>(c, 4, g, grid, stream, "gemm_2cta_n256_s5_tmastore");
-        if (bn == 256) return launch_gemm<2, 256, 5, false>(c, 5, g, grid, stream, "gemm_2cta_n256_s5_direct");
-        if (epilogue == 2) return launch_gemm<2, 128, 6, true>(c, 6, g, grid, stream, "gemm_2cta_n128_s6_tmastore");
-        return launch_gemm<2, 128, 7, false>(c, 7, g, grid, stream, "gemm_2cta_n128_s7_direct");
+        if (bn == 256 && epilogue == 2) return launch_gemm<2, 256, 5, true, 32>(c, 4, g, grid, stream, "gemm_2cta_n256_s5_tmastore");
+        if (bn == 256) return launch_gemm<2, 256, 5, false, 32>(c, 5, g, grid, stream, "gemm_2cta_n256_s5_direct");
+        if (epilogue == 2) return launch_gemm<2, 128, 6, true, 32>(c, 6, g, grid, stream, "gemm_2cta_n128_s6_tmastore");
+        return launch_gemm<2, 128, 6, false, 32>(c, 7, g, grid, stream, "gemm_2cta_n128_s6_direct");
     }
-    if (bn == 128 && epilogue == 2) return launch_gemm<1, 128, 5, true>(c, 0, g, grid, stream, "gemm_1cta_n128_s5_tmastore");
-    if (bn == 128) return launch_gemm<1, 128, 6, false>(c, 1, g, grid, stream, "gemm_1cta_n128_s6_direct");
-    if (epilogue == 2) return launch_gemm<1, 256, 3, true>(c, 2, g, grid, stream, "gemm_1cta_n256_s3_tmastore");
-    return launch_gemm<1, 256, 4, false>(c, 3, g, grid, stream, "gemm_1cta_n256_s4_direct");
+    if (bn == 128 && epilogue == 2) return launch_gemm<1, 128, 5, true, 32>(c, 0, g, grid, stream, "gemm_1cta_n128_s5_tmastore");
+    if (bn == 128) return launch_gemm<1, 128, 4, false, 64>(c, 1, g, grid, stream, "gemm_1cta_n128_s4_direct");
+    if (epilogue == 2) return launch_gemm<1, 256, 3, true, 32>(c, 2, g, grid, stream, "gemm_1cta_n256_s3_tmastore");
+    return launch_gemm<1, 256, 3, false, 48>(c, 3, g, grid, stream, "gemm_1cta_n256_s3_direct");
 }
 
 int nvfp4_gemv(const nvfp4_problem* p, void* stream_v) {
@@ -435,7 +528,7 @@ int nvfp4_debug_read_trace(unsigned long long* out, int n_ctas) {
     if (int rc = get_ctx(&c)) return rc;
     if (!c->trace || n_ctas > kMaxCtas) return fail(NVFP4_ERR_INVALID_ARGUMENT, "no trace buffer");
     CUDA_TRY(cudaDeviceSynchronize());
-    CUDA_TRY(cudaMemcpy(out, c->trace, static_cast<size_t>(n_ctas) * 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    CUDA_TRY(cudaMemcpy(out, c->trace, static_cast<size_t>(n_ctas) * 16 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
     return NVFP4_OK;
 }
 #endif

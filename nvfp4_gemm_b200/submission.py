@@ -66,12 +66,13 @@ def custom_kernel(data: input_t) -> output_t:
     return data[6]
 
 
-def gemm(data: input_t, tile_n: int = 0, epilogue: int = 0, grid: int = 0, cta_group: int = 0) -> output_t:
+def gemm(data: input_t, tile_n: int = 0, epilogue: int = 0, grid: int = 0, cta_group: int = 0,
+         split_k: int = 0) -> output_t:
     """The GEMM with an explicit kernel configuration (tests and tuning)."""
     lib = _lib.load()
     _require_cuda(data)
     problem = make_problem(data)
-    cfg = GemmConfig(tile_n, epilogue, grid, cta_group)
+    cfg = GemmConfig(tile_n, epilogue, grid, cta_group, split_k)
     stream = torch.cuda.current_stream(data[0].device).cuda_stream
     with torch.cuda.device(data[0].device):
         _lib.check(lib.nvfp4_gemm(problem, cfg, stream))

@@ -37,22 +37,44 @@ def test_custom_kernel_matches_oracle_bit_exact(sub, oracle, shape):
     assert_bit_exact(out, expected_fp16(oracle, data), what=f"{shape} {sub.last_kernel()}")
 
 
-@pytest.mark.parametrize("tile_n,epilogue", [(128, 1), (128, 2), (256, 1), (256, 2)])
-@pytest.mark.parametrize("shape,grid", [((128, 512, 4096, 1), 3), ((300, 768, 1536, 2), 0), ((512, 1024, 1024, 1), 5),
-                                        ((128, 256, 256, 1), 0)])
-def test_every_kernel_variant_and_split_pattern(sub, oracle, tile_n, epilogue, shape, grid):
+VARIANTS = [  # (cta_group, tile_n, epilogue, split_k)
+    (1, 128, 1, 1), (1, 128, 2, 1), (1, 256, 1, 1), (1, 256, 2, 1),     # one CTA per tile, stream-K
+    (2, 128, 1, 1), (2, 128, 2, 1), (2, 256, 1, 1), (2, 256, 2, 1),     # CTA pair per 256-row tile
+]
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+@pytest.mark.parametrize("shape,grid", [((128, 512, 4096, 1), 6), ((300, 768, 1536, 2), 0), ((512, 1024, 1024, 1), 10),
+                                        ((256, 256, 256, 1), 0), ((640, 512, 2048, 1), 4)])
+def test_every_kernel_variant_and_split_pattern(sub, oracle, variant, shape, grid):
     from nvfp4_gemm_b200.inputs import generate_input
+    cta_group, tile_n, epilogue, split_k = variant
     m, n, k, l = shape
     data = generate_input(m, n, k, l, 7)
     data[6].view(torch.int16).fill_(0x7fff)
-    sub.gemm(data, tile_n=tile_n, epilogue=epilogue, grid=grid)
+    kw = dict(tile_n=tile_n, epilogue=epilogue, grid=grid, cta_group=cta_group, split_k=split_k)
+    sub.gemm(data, **kw)
     sub.check_status()
     assert_bit_exact(data[6], expected_fp16(oracle, data), what=f"{shape} {sub.last_kernel()} grid={grid}")
-    # run it again: the scratch slots must have been left zeroed by the previous launch
+    # run it again: the per-tile counters must have been left at zero by the previous launch
     data[6].view(torch.int16).fill_(0x7fff)
-    sub.gemm(data, tile_n=tile_n, epilogue=epilogue, grid=grid)
+    sub.gemm(data, **kw)
     sub.check_status()
     assert_bit_exact(data[6], expected_fp16(oracle, data), what=f"second launch {shape}")
+
+
+@pytest.mark.parametrize("split_k", [2, 4])
+@pytest.mark.parametrize("shape", [(128, 256, 2048, 1), (77, 384, 2304, 2), (128, 512, 1024, 1), (1, 128, 1280, 1), (200, 256, 2048, 1)])
+def test_cluster_split_k(sub, oracle, split_k, shape):
+    """K split across a cluster, partial sums exchanged through distributed shared memory."""
+    from nvfp4_gemm_b200.inputs import generate_input
+    m, n, k, l = shape
+    data = generate_input(m, n, k, l, 21)
+    data[6].view(torch.int16).fill_(0x7fff)
+    sub.gemm(data, split_k=split_k)
+    sub.check_status()
+    assert sub.last_kernel().startswith(f"gemm_splitk{split_k}")
+    assert_bit_exact(data[6], expected_fp16(oracle, data), what=f"{shape} {sub.last_kernel()}")
 
 
 def test_largest_reference_test_shape(sub, oracle):
