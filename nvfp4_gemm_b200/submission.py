@@ -56,13 +56,34 @@ def _require_cuda(data: input_t) -> None:
         raise ValueError("custom_kernel needs CUDA tensors (there is no CPU fallback)")
 
 
+_problem_cache: dict = {}
+
+
+def _cached_problem(data: input_t) -> Problem:
+    """make_problem() is ~40 attribute reads; harnesses call with the same tensors over and over,
+    so remember the translated struct by the tensors' addresses and shapes."""
+    a, b, _, _, sfa_perm, sfb_perm, c = data
+    key = (a.data_ptr(), b.data_ptr(), c.data_ptr(), sfa_perm.data_ptr(), sfb_perm.data_ptr(), data[2].data_ptr(),
+           data[3].data_ptr(), a.shape, b.shape, c.stride())
+    hit = _problem_cache.get(key)
+    if hit is None:
+        _require_cuda(data)
+        if len(_problem_cache) > 256:
+            _problem_cache.clear()
+        hit = _problem_cache[key] = make_problem(data)
+    return hit
+
+
 def custom_kernel(data: input_t) -> output_t:
     lib = _lib.load()
-    _require_cuda(data)
-    problem = make_problem(data)
-    stream = torch.cuda.current_stream(data[0].device).cuda_stream
-    with torch.cuda.device(data[0].device):
+    problem = _cached_problem(data)
+    dev = data[0].device
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    if torch.cuda.current_device() == dev.index:
         _lib.check(lib.nvfp4_matmul(problem, stream))
+    else:
+        with torch.cuda.device(dev):
+            _lib.check(lib.nvfp4_matmul(problem, stream))
     return data[6]
 
 
