@@ -85,6 +85,34 @@ int nvfp4_gemv(const nvfp4_problem* problem, void* stream);
 int nvfp4_matmul(const nvfp4_problem* problem, void* stream);
 
 /*
+ * The same GEMM for callers that cannot allocate device memory when they call: code that runs
+ * while another thread captures a CUDA graph in global capture mode (cudaMalloc is illegal
+ * then), services that hand all free HBM to their own pool at start-up so that a later
+ * cudaMalloc fails, and latency-critical loops that may not take the allocator's lock.
+ * It has no counterpart in the reference.
+ *
+ * nvfp4_gemm() keeps the fp32 partial sums of tiles that several persistent CTAs share in
+ * scratch memory it allocates on first use.  This entry point runs the same persistent kernel
+ * (128 x 128 tiles, one CTA per worker) with that scratch in a fixed array inside the library's
+ * device image: 8 MiB (two 64 KiB slots for each of at most 64 workers) that every GPU which
+ * loads the library holds until the process exits.  Nothing is allocated or freed, on the device
+ * or through any allocating library routine; tensor maps are encoded into stack storage.
+ *
+ *   workers   persistent CTAs to use; 0 = 64, the most the fixed scratch has slots for.  A
+ *             larger request is rejected with NVFP4_ERR_INVALID_ARGUMENT (so is any shape
+ *             nvfp4_gemm() would reject).  Fewer CTAs than SMs: expect lower throughput than
+ *             nvfp4_gemm() on large problems.
+ *
+ * The first call on a device looks up the array's device address and raises the kernel's
+ * shared-memory limit; make that first call outside any stream capture.  All calls on a device
+ * share the one array, which keeps the last call's contents: each call re-zeroes the tile
+ * counters on `stream` before its kernel, and two calls whose kernels overlap on the GPU
+ * (different streams, no dependency) race on the slots -- serialise them.  A bounded wait that
+ * runs out inside this variant is recorded in device memory only (the kernel still returns).
+ */
+int nvfp4_gemm_static_scratch(const nvfp4_problem* problem, int workers, void* stream);
+
+/*
  * Waits for `stream` and returns NVFP4_ERR_DEVICE_TIMEOUT if any kernel launched by this
  * library on the current device reported a timed-out wait since the last check, else NVFP4_OK.
  * The reference has no counterpart (its waits are unbounded spins, s_128t.py:124-183,309-319).

@@ -19,7 +19,7 @@ NVFP4_ERR_UNSUPPORTED = -4
 EXPORTED_SYMBOLS = (
     "nvfp4_gemm", "nvfp4_gemv", "nvfp4_matmul", "nvfp4_check_status", "nvfp4_set_wait_timeout_ns",
     "nvfp4_selftest_bounded_wait", "nvfp4_scratch_bytes", "nvfp4_launch_count", "nvfp4_last_kernel",
-    "nvfp4_shutdown", "nvfp4_last_error", "nvfp4_version", "nvfp4_plan_units",
+    "nvfp4_shutdown", "nvfp4_last_error", "nvfp4_version", "nvfp4_plan_units", "nvfp4_gemm_static_scratch",
 )
 
 
@@ -64,6 +64,8 @@ def load() -> ctypes.CDLL:
     lib = ctypes.CDLL(str(LIB_PATH))
     lib.nvfp4_gemm.argtypes = [ctypes.POINTER(Problem), ctypes.POINTER(GemmConfig), c_void_p]
     lib.nvfp4_gemm.restype = c_int
+    lib.nvfp4_gemm_static_scratch.argtypes = [ctypes.POINTER(Problem), c_int, c_void_p]
+    lib.nvfp4_gemm_static_scratch.restype = c_int
     lib.nvfp4_gemv.argtypes = [ctypes.POINTER(Problem), c_void_p]
     lib.nvfp4_gemv.restype = c_int
     lib.nvfp4_matmul.argtypes = [ctypes.POINTER(Problem), c_void_p]

@@ -558,6 +558,147 @@ void nvfp4_shutdown(void) {
     if (prev >= 0) cudaSetDevice(prev);
 }
 
+// ---------------------------------------------------------------------------------------------
+// GEMM for callers that must not allocate: the partial-tile scratch of the persistent kernel
+// lives in a fixed device array that is part of this library's image.
+// ---------------------------------------------------------------------------------------------
+}  // extern "C"
+
+namespace {
+
+constexpr int kStaticMaxWorkers = 64;  // persistent CTAs the fixed scratch has slots for
+// Two 128 x 128 fp32 partial-tile slots per worker: 64 * 2 * 64 KiB = 8 MiB, resident on every
+// GPU that loads the library, until the process exits.
+static __device__ __align__(256) float g_static_scratch[kStaticMaxWorkers * 2 * kBM * 128];
+static __device__ __align__(256) int g_static_counters[kStaticMaxWorkers];
+static __device__ __align__(256) int g_static_status[4];
+
+// What host code may use of the arrays above: their device addresses, looked up once per device.
+// (In host code the array names are only handles for the symbol lookup, never pointers.)
+struct StaticScratch {
+    bool ready = false;
+    float* scratch = nullptr;
+    int* counters = nullptr;
+    int* status = nullptr;
+    int num_sms = 0;
+};
+StaticScratch g_static[64];
+std::mutex g_static_mutex;
+EncodeTiledFn g_static_encode = nullptr;
+
+int static_scratch_setup(int dev, StaticScratch** out) {
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    StaticScratch& st = g_static[dev];
+    if (!st.ready) {
+        // the calling thread's current device is `dev`: the lookups below resolve that device's copy
+        CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&st.scratch), g_static_scratch));
+        CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&st.counters), g_static_counters));
+        CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&st.status), g_static_status));
+        int major = 0;
+        CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+        if (major != 10) return fail(NVFP4_ERR_UNSUPPORTED, "device %d is not sm_100", dev);
+        CUDA_TRY(cudaDeviceGetAttribute(&st.num_sms, cudaDevAttrMultiProcessorCount, dev));
+        CUDA_TRY(cudaFuncSetAttribute(gemm_nvfp4_kernel<1, 128, 4, false, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      GemmSmem<1, 128, 4, false, 64>::kDynamicBytes));
+        st.ready = true;
+    }
+    if (!g_static_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        if (!fn || qres != cudaDriverEntryPointSuccess)
+            return fail(NVFP4_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+        g_static_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    *out = &st;
+    return NVFP4_OK;
+}
+
+// Encodes a tensor map into caller storage (no cache: nothing is kept on the heap).
+int encode_map_inplace(const MapKey& key, CUtensorMap* out) {
+    cuuint64_t dims[4] = {key.dims[0], key.dims[1], key.dims[2], key.dims[3]};
+    cuuint64_t strides[3] = {key.strides[0], key.strides[1], key.strides[2]};
+    cuuint32_t box[4] = {key.box[0], key.box[1], key.box[2], key.box[3]};
+    cuuint32_t elem[4] = {1, 1, 1, 1};
+    CUresult r = g_static_encode(out, static_cast<CUtensorMapDataType>(key.dtype), key.rank, const_cast<void*>(key.ptr), dims,
+                                 strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, static_cast<CUtensorMapSwizzle>(key.swizzle),
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(NVFP4_ERR_CUDA, "cuTensorMapEncodeTiled failed (CUresult %d)", static_cast<int>(r));
+    return NVFP4_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int nvfp4_gemm_static_scratch(const nvfp4_problem* p, int workers, void* stream_v) {
+    if (int rc = validate_common(p)) return rc;
+    if (!p->sfa_perm || !p->sfb_perm)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "the GEMM needs the permuted scale tensors (sfa_perm, sfb_perm)");
+    if (p->k % kKPerStage) return fail(NVFP4_ERR_INVALID_ARGUMENT, "k must be a multiple of 256 (got %d)", p->k);
+    if (p->n % 128) return fail(NVFP4_ERR_INVALID_ARGUMENT, "n must be a multiple of 128 (got %d)", p->n);
+    if (!aligned(p->a, 16) || !aligned(p->b, 16) || !aligned(p->c, 16) || !aligned(p->sfa_perm, 16) || !aligned(p->sfb_perm, 16))
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "a, b, c, sfa_perm and sfb_perm must be 16-byte aligned");
+    if (p->a_row_stride % 16 || p->b_row_stride % 16 || p->a_row_stride < p->k / 2 || p->b_row_stride < p->k / 2)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "row strides of a and b must be multiples of 16 bytes and >= k/2");
+    if (p->c_row_stride % 8 || p->c_row_stride < p->n)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "c_row_stride must be a multiple of 8 elements and >= n");
+    if (p->l > 1 && (p->a_batch_stride % 16 || p->b_batch_stride % 16 || p->c_batch_stride % 8 ||
+                     p->sfa_perm_batch_stride % 16 || p->sfb_perm_batch_stride % 16))
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "batch strides must keep 16-byte alignment");
+    if (workers < 0 || workers > kStaticMaxWorkers)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT,
+                    "workers = %d exceeds what the fixed scratch holds: at most %d persistent CTAs (8 MiB of partial-tile slots)",
+                    workers, kStaticMaxWorkers);
+
+    int dev = -1;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(NVFP4_ERR_CUDA, "unexpected device ordinal %d", dev);
+    StaticScratch* st = nullptr;
+    if (int rc = static_scratch_setup(dev, &st)) return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+    constexpr int bn = 128;
+    GemmParams g;
+    std::memset(&g, 0, sizeof(g));
+    g.M = p->m; g.N = p->n; g.K = p->k; g.L = p->l;
+    g.tiles_m = (p->m + kBM - 1) / kBM;
+    g.tiles_n = p->n / bn;
+    g.k_tiles = p->k / kKPerStage;
+    const long long units = static_cast<long long>(g.tiles_m) * g.tiles_n * p->l * g.k_tiles;
+    if (units > 0x7fffffffLL) return fail(NVFP4_ERR_INVALID_ARGUMENT, "problem too large: %lld work units", units);
+    g.total_units = static_cast<int>(units);
+    g.c = static_cast<__half*>(p->c);
+    g.scratch = st->scratch;
+    g.counters = st->counters;
+    g.status = st->status;
+    g.c_row_stride = p->c_row_stride;
+    g.c_batch_stride = p->c_batch_stride;
+    g.timeout_cycles = g_timeout_ns.load() * 2;
+
+    const uint64_t kbytes = static_cast<uint64_t>(p->k) / 2;
+    const uint64_t a_bs = p->l > 1 ? static_cast<uint64_t>(p->a_batch_stride) : static_cast<uint64_t>(p->a_row_stride) * p->m;
+    const uint64_t b_bs = p->l > 1 ? static_cast<uint64_t>(p->b_batch_stride) : static_cast<uint64_t>(p->b_row_stride) * p->n;
+    if (int rc = encode_map_inplace(make_key(p->a, kbytes, p->m, p->l, p->a_row_stride, a_bs, kBKBytes, kBM, CU_TENSOR_MAP_DATA_TYPE_UINT8), &g.tma_a)) return rc;
+    if (int rc = encode_map_inplace(make_key(p->b, kbytes, p->n, p->l, p->b_row_stride, b_bs, kBKBytes, bn, CU_TENSOR_MAP_DATA_TYPE_UINT8), &g.tma_b)) return rc;
+    if (int rc = encode_map_inplace(make_sf_key(p->sfa_perm, p->m, p->k, p->l, p->sfa_perm_batch_stride, 1), &g.tma_sfa)) return rc;
+    if (int rc = encode_map_inplace(make_sf_key(p->sfb_perm, p->n, p->k, p->l, p->sfb_perm_batch_stride, 1), &g.tma_sfb)) return rc;
+
+    int grid = workers > 0 ? workers : kStaticMaxWorkers;
+    if (grid > st->num_sms) grid = st->num_sms;
+    if (grid > g.total_units) grid = g.total_units;
+
+    // The array keeps whatever the previous call left: the slots are always written before they
+    // are read, but the per-tile counters must start at zero (an aborted launch may have left some).
+    CUDA_TRY(cudaMemsetAsync(st->counters, 0, kStaticMaxWorkers * sizeof(int), stream));
+    using S = GemmSmem<1, 128, 4, false, 64>;
+    gemm_nvfp4_kernel<1, 128, 4, false, 64><<<grid, kGemmThreads, S::kDynamicBytes, stream>>>(g);
+    CUDA_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    t_last_kernel = "gemm_1cta_n128_s4_direct(static scratch)";
+    return NVFP4_OK;
+}
+
 const char* nvfp4_last_error(void) { return t_error.c_str(); }
 
 const char* nvfp4_version(void) { return "nvfp4_b200 0.1 (sm_100a)"; }
