@@ -85,6 +85,23 @@ int nvfp4_gemv(const nvfp4_problem* problem, void* stream);
 int nvfp4_matmul(const nvfp4_problem* problem, void* stream);
 
 /*
+ * Column-parallel multi-GPU GEMM, last step: an all-gather of per-rank fp16 column blocks leaves
+ * [blocks][rows][n_local] in memory; this writes the row-major [rows][blocks * n_local] matrix
+ * (row stride dst_row_stride elements).  The reference has no multi-GPU code; no counterpart.
+ */
+int nvfp4_interleave_column_blocks(const void* src, void* dst, int64_t rows, int32_t n_local, int32_t blocks,
+                                   int64_t dst_row_stride, void* stream);
+
+/*
+ * Plain scale factors [l][rows][k/16] (strides in bytes) -> the permuted 128 x 4 atom layout the
+ * GEMM reads ([32,4,rest_rows,4,rest_k,l], ref.txt:31, s_128t.py:554-562), rows zero-padded to a
+ * multiple of 128.  The reference receives both forms from its harness (template.py:11-14) and has
+ * no converter of its own.
+ */
+int nvfp4_permute_scales(const void* plain, void* permuted, int32_t rows, int32_t k, int32_t l, int64_t plain_row_stride,
+                         int64_t plain_batch_stride, int64_t permuted_batch_stride, void* stream);
+
+/*
  * The same GEMM for callers that cannot allocate device memory when they call: code that runs
  * while another thread captures a CUDA graph in global capture mode (cudaMalloc is illegal
  * then), services that hand all free HBM to their own pool at start-up so that a later

@@ -14,6 +14,7 @@
 
 #include "gemm_sm100.cuh"
 #include "gemv_sm100.cuh"
+#include "layout_kernels.cuh"
 
 namespace {
 
@@ -470,6 +471,50 @@ int nvfp4_gemv(const nvfp4_problem* p, void* stream_v) {
     CUDA_TRY(cudaGetLastError());
     g_launches.fetch_add(1);
     t_last_kernel = "gemv_warp_r2";
+    return NVFP4_OK;
+}
+
+int nvfp4_interleave_column_blocks(const void* src, void* dst, int64_t rows, int32_t n_local, int32_t blocks,
+                                   int64_t dst_row_stride, void* stream_v) {
+    if (!src || !dst) return fail(NVFP4_ERR_INVALID_ARGUMENT, "src and dst must not be NULL");
+    if (rows < 1 || n_local < 8 || n_local % 8 || blocks < 1)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "rows >= 1, n_local a positive multiple of 8, blocks >= 1 required");
+    if (dst_row_stride % 8 || dst_row_stride < static_cast<int64_t>(n_local) * blocks)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "dst_row_stride must be a multiple of 8 elements and >= n_local * blocks");
+    if (!aligned(src, 16) || !aligned(dst, 16)) return fail(NVFP4_ERR_INVALID_ARGUMENT, "src and dst must be 16-byte aligned");
+    int dev = 0, sms = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const long long total = rows * (n_local / 8) * blocks;
+    long long grid = (total + 255) / 256;
+    if (grid > static_cast<long long>(sms) * 16) grid = static_cast<long long>(sms) * 16;
+    interleave_column_blocks_kernel<<<static_cast<int>(grid), 256, 0, static_cast<cudaStream_t>(stream_v)>>>(
+        static_cast<const uint4*>(src), static_cast<uint4*>(dst), rows, n_local / 8, blocks, dst_row_stride / 8);
+    CUDA_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    return NVFP4_OK;
+}
+
+int nvfp4_permute_scales(const void* plain, void* permuted, int32_t rows, int32_t k, int32_t l, int64_t plain_row_stride,
+                         int64_t plain_batch_stride, int64_t permuted_batch_stride, void* stream_v) {
+    if (!plain || !permuted) return fail(NVFP4_ERR_INVALID_ARGUMENT, "plain and permuted must not be NULL");
+    if (rows < 1 || l < 1 || k < 64 || k % 64) return fail(NVFP4_ERR_INVALID_ARGUMENT, "rows, l >= 1 and k a positive multiple of 64 required");
+    if (!aligned(plain, 4) || !aligned(permuted, 16) || plain_row_stride % 4 || plain_row_stride < k / 16)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "plain must be 4-byte aligned with a row stride that is a multiple of 4 and >= k/16; permuted 16-byte aligned");
+    const long long need = static_cast<long long>((rows + 127) / 128) * (k / 64) * 512;
+    if (l > 1 && (permuted_batch_stride < need || permuted_batch_stride % 16 || plain_batch_stride % 4))
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "batch strides too small or misaligned");
+    int dev = 0, sms = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const long long total = need / 16 * l;
+    long long grid = (total + 255) / 256;
+    if (grid > static_cast<long long>(sms) * 16) grid = static_cast<long long>(sms) * 16;
+    permute_scales_kernel<<<static_cast<int>(grid), 256, 0, static_cast<cudaStream_t>(stream_v)>>>(
+        static_cast<const uint8_t*>(plain), static_cast<uint8_t*>(permuted), rows, k / 16, plain_row_stride, plain_batch_stride,
+        permuted_batch_stride, l);
+    CUDA_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
     return NVFP4_OK;
 }
 

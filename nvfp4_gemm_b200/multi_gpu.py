@@ -1,0 +1,245 @@
+"""Column-parallel NVFP4 GEMM over the GPUs of one node (one process per GPU).
+
+Only the large GEMM is partitioned.  Rank r holds all of ``a`` (+ its scales) and rows
+[r*N/g, (r+1)*N/g) of ``b`` with the matching row blocks of the permuted ``sfb``; it computes
+C[:, r*N/g:(r+1)*N/g] with the single-GPU kernel, and the fp16 column blocks are all-gathered with
+NCCL over NVLink.  The output columns are independent, so the all-gather is the only exchange.
+
+The all-gather wants contiguous per-rank chunks, but a column block is strided inside row-major C.
+Each rank therefore computes into a contiguous staging block [rows, N/g], the gather lands as
+[g][rows][N/g], and one HBM-bound kernel (``nvfp4_interleave_column_blocks``) writes [rows][N].
+The rows are processed in panels so that the GEMM of panel i+1 overlaps the gather and the
+re-layout of panel i (NCCL runs on the process group's own stream).
+
+The reference has no multi-GPU code; this follows the operator contract of template.py:4-25 on
+each rank.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass(frozen=True)
+class ColumnShard:
+    rank: int
+    world: int
+    n_total: int
+
+    @property
+    def n_local(self) -> int:
+        return self.n_total // self.world
+
+    @property
+    def begin(self) -> int:
+        return self.rank * self.n_local
+
+    @property
+    def end(self) -> int:
+        return self.begin + self.n_local
+
+
+def plan_shard(n: int, world: int, rank: int) -> ColumnShard:
+    """Equal column blocks; each must be whole 128-row scale blocks (the permuted SFB is sliced by block)."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"bad rank {rank} of {world}")
+    if n % (128 * world):
+        raise ValueError(f"N = {n} must be a multiple of 128 * world_size = {128 * world}")
+    return ColumnShard(rank, world, n)
+
+
+def shard_inputs(data, shard: ColumnShard):
+    """Slice the full 7-tuple down to this rank's operands (views, nothing is copied):
+    all of a/sfa, rows [begin, end) of b/sfb, row blocks [begin/128, end/128) of sfb_permuted."""
+    a, b, sfa, sfb, sfa_perm, sfb_perm, c = data
+    rb0, rb1 = shard.begin // 128, shard.end // 128
+    return (a, b[shard.begin:shard.end], sfa, sfb[shard.begin:shard.end], sfa_perm, sfb_perm[:, :, rb0:rb1], c)
+
+
+def row_panels(m: int, panels: int):
+    """Split M into at most `panels` ranges of whole 256-row tiles."""
+    tiles = (m + 255) // 256
+    panels = max(1, min(panels, tiles))
+    out, start = [], 0
+    for p in range(panels):
+        t = tiles // panels + (1 if p < tiles % panels else 0)
+        end = min(m, start + t * 256)
+        if end > start:
+            out.append((start, end))
+        start = end
+    return out
+
+
+def to_device_same_layout(t: torch.Tensor, device) -> torch.Tensor:
+    """Copy a dense (possibly permuted) tensor to `device` byte for byte, keeping its strides: the
+    permuted scale tensors are defined by their memory layout, which a logical copy could change."""
+    raw = t.view(torch.uint8) if t.element_size() == 1 else t
+    flat = torch.as_strided(raw, (t.numel(),), (1,), raw.storage_offset())
+    moved = flat.to(device)
+    out = torch.as_strided(moved, tuple(t.shape), tuple(t.stride()), 0)
+    return out.view(t.dtype) if t.element_size() == 1 else out
+
+
+def _default_gemm(panel_data):
+    from .submission import custom_kernel
+    return custom_kernel(panel_data)
+
+
+def _default_interleave(src: torch.Tensor, dst: torch.Tensor, rows: int, n_local: int, blocks: int, dst_row_stride: int):
+    from . import _lib
+    lib = _lib.load()
+    _lib.check(lib.nvfp4_interleave_column_blocks(src.data_ptr(), dst.data_ptr(), rows, n_local, blocks, dst_row_stride,
+                                                  torch.cuda.current_stream(dst.device).cuda_stream))
+
+
+class ColumnParallelGemm:
+    """Reusable plan + buffers for one problem shape on one rank.
+
+    ``gemm_fn`` and ``interleave_fn`` exist so that the host logic can be exercised on CPU ranks
+    (gloo) with stand-ins; the defaults are the CUDA library.
+    """
+
+    def __init__(self, m: int, n: int, k: int, group=None, device=None, panels: int = 4,
+                 gemm_fn: Optional[Callable] = None, interleave_fn: Optional[Callable] = None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.shard = plan_shard(n, self.world, self.rank)
+        self.m, self.n, self.k = m, n, k
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.panels = row_panels(m, panels)
+        self.gemm_fn = gemm_fn or _default_gemm
+        self.interleave_fn = interleave_fn or _default_interleave
+        nl = self.shard.n_local
+        # staging [1][m][n_local] (the operator's c layout with l = 1) and gather target per panel
+        self.staging = torch.empty((1, m, nl), dtype=torch.float16, device=self.device)
+        self.gathered = [torch.empty((self.world, p1 - p0, nl), dtype=torch.float16, device=self.device)
+                         for (p0, p1) in self.panels]
+
+    def __call__(self, local_data, c_full: torch.Tensor) -> torch.Tensor:
+        """local_data: this rank's 7-tuple (its ``c`` entry is ignored); c_full: [M, N, 1] fp16, row-major."""
+        a, b, sfa, sfb, sfa_perm, sfb_perm, _ = local_data
+        if a.shape[2] != 1:
+            raise ValueError("the column-parallel path handles l = 1")
+        nl = self.shard.n_local
+        works = []
+        for idx, (p0, p1) in enumerate(self.panels):
+            rb0, rb1 = p0 // 128, (p1 + 127) // 128
+            c_panel = self.staging[:, p0:p1, :].permute(1, 2, 0)          # [rows, n_local, 1]
+            panel = (a[p0:p1], b, sfa[p0:p1], sfb, sfa_perm[:, :, rb0:rb1], sfb_perm, c_panel)
+            self.gemm_fn(panel)
+            works.append(dist.all_gather_into_tensor(self.gathered[idx].view(-1, nl), self.staging[0, p0:p1, :], group=self.group,
+                                                     async_op=True))
+            if idx > 0:
+                self._finish_panel(idx - 1, works[idx - 1], c_full)
+        self._finish_panel(len(self.panels) - 1, works[-1], c_full)
+        return c_full
+
+    def _finish_panel(self, idx: int, work, c_full: torch.Tensor):
+        p0, p1 = self.panels[idx]
+        work.wait()   # makes the current stream wait for the collective; the host does not block on CUDA
+        dst = c_full[p0:p1]
+        self.interleave_fn(self.gathered[idx], dst, p1 - p0, self.shard.n_local, self.world, c_full.stride(0))
+
+
+def bench_column_parallel(args, w, rank, world, dev, ClockSampler, measured_peaks, algorithmic_flops):
+    """`bench.py --gpus N` for N > 1: strong scaling of the one partitioned workload."""
+    import json
+    from .inputs import generate_input
+    from . import submission as S
+
+    m, n, k = w["m"], w["n"], w["k"]
+    shard = plan_shard(n, world, rank)
+    # every rank builds the same full B from the seed and keeps its rows (inputs are synthetic)
+    n_sets = 2
+    sets = []
+    for i in range(n_sets):
+        full = generate_input(m, n, k, 1, 1111 + i, device="cpu")
+        local = shard_inputs(full, shard)
+        sets.append(tuple(to_device_same_layout(t, dev) if j < 6 else None for j, t in enumerate(local)))
+        del full
+    c_full = [torch.empty((1, m, n), dtype=torch.float16, device=dev).permute(1, 2, 0) for _ in range(n_sets)]
+    plan = ColumnParallelGemm(m, n, k, device=dev, panels=4)
+
+    def step(i):
+        plan(sets[i % n_sets], c_full[i % n_sets])
+
+    for i in range(args.warmup):
+        step(i)
+    S.check_status()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+
+    parity = None
+    if rank == 0:
+        # sampled rows of the gathered result against the CPU oracle (all N columns, so every
+        # rank's block and the re-layout are covered)
+        import numpy as np
+        from oracle import nvfp4_oracle as O
+        step(0)
+        torch.cuda.synchronize()
+        full = generate_input(m, n, k, 1, 1111, device="cpu")
+        rows = np.sort(np.random.default_rng(0).choice(m, 16, replace=False))
+        a_np, b_np, sfa_np, sfb_np = O.tensors_to_numpy(full)
+        exp = O.ref_gemm_c(a_np[rows], b_np, sfa_np[rows], sfb_np)
+        got = c_full[0][torch.from_numpy(rows).to(dev)].cpu().numpy()
+        parity = "bit-exact on 16 sampled rows x all columns" if np.array_equal(got.view(np.uint16), exp.view(np.uint16)) else "MISMATCH"
+        del full
+    dist.barrier()
+
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    launches0 = S.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    launches = S.launch_count() - launches0
+    clocks = sampler.stop()
+    S.check_status()
+
+    # GEMM-only time of this rank's block, for the split of compute vs exchange
+    torch.cuda.synchronize()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    local = sets[0][:6] + (plan.staging.permute(1, 2, 0),)
+    S.custom_kernel(local)
+    g0.record()
+    for _ in range(5):
+        S.custom_kernel(local)
+    g1.record()
+    torch.cuda.synchronize()
+    gemm_ms = torch.tensor([g0.elapsed_time(g1) / 5], device=dev)
+    dist.all_reduce(gemm_ms, op=dist.ReduceOp.MAX)
+
+    if rank == 0:
+        ms_per_step = float(ms.item()) / args.steps
+        flops = algorithmic_flops(w)
+        tflops = flops / (ms_per_step * 1e-3) / 1e12
+        gather_bytes = (world - 1) / world * m * n * 2
+        line = dict(metric="nvfp4_matmul_throughput", value=tflops, unit="TFLOP/s", n_gpus=world, steps=args.steps,
+                    warmup=args.warmup, ms_per_step=ms_per_step, higher_is_better=True, scaling="strong", vs_baseline=None,
+                    dtype="e2m1 x ue4m3 -> f32 -> f16", data="synthetic",
+                    config=dict(workload=w["name"], parallelism=f"column-parallel over N on {world} GPUs, NCCL all-gather of fp16 blocks, 4 row panels",
+                                timing="CUDA events, max over ranks; 2 rotating input sets (302 MB per rank set) > L2",
+                                gemm_only_ms_per_rank=float(gemm_ms.item()),
+                                gemm_only_tflops_per_gpu=flops / world / (float(gemm_ms.item()) * 1e-3) / 1e12,
+                                allgather_bytes_in_per_gpu=gather_bytes, parity_vs_oracle=parity,
+                                nvlink_bound_ms=gather_bytes / 770e9 * 1e3),
+                    roofline=dict(bound="nvlink", achieved=gather_bytes / (ms_per_step * 1e-3) / 1e9, peak=770.0, unit="GB/s",
+                                  frac=gather_bytes / (ms_per_step * 1e-3) / 1e9 / 770.0, traffic=None,
+                                  peak_source="measured peer copy per direction"),
+                    e2e=dict(value=tflops, unit="TFLOP/s", ms_per_step=ms_per_step, h2d_bytes_per_step=0, d2h_bytes_per_step=0,
+                             note="inputs resident; the gathered fp16 C (all N columns) is the step's result on every rank"),
+                    gpu_launches=int(launches), clocks=clocks)
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
