@@ -175,13 +175,13 @@ def bench_column_parallel(args, w, rank, world, dev, ClockSampler, measured_peak
     torch.cuda.synchronize()
 
     parity = None
+    step(0)                      # every rank takes part in the collective; rank 0 then checks the result
+    torch.cuda.synchronize()
     if rank == 0:
         # sampled rows of the gathered result against the CPU oracle (all N columns, so every
         # rank's block and the re-layout are covered)
         import numpy as np
         from oracle import nvfp4_oracle as O
-        step(0)
-        torch.cuda.synchronize()
         full = generate_input(m, n, k, 1, 1111, device="cpu")
         rows = np.sort(np.random.default_rng(0).choice(m, 16, replace=False))
         a_np, b_np, sfa_np, sfb_np = O.tensors_to_numpy(full)
