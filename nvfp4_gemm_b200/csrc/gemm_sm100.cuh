@@ -468,23 +468,33 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                     // 64 columns (128 bytes of fp16) at a time through a swizzled 32-row staging buffer.
                     uint8_t* staging_gen = smem_gen + S::kEpiOff + (warp - 2) * S::kStagingPerWarp;
                     const uint32_t staging = smem_base + S::kEpiOff + (warp - 2) * S::kStagingPerWarp;
-#pragma unroll 1
-                    for (int c0 = 0; c0 < BN; c0 += 64) {
-                        uint32_t v[2][32];
-                        ptx::tc_ld_32cols(t_acc + c0, v[0]);
-                        ptx::tc_ld_32cols(t_acc + c0 + 32, v[1]);
+                    // Software-pipelined: the TMEM loads of chunk i+1 are in flight while chunk i is
+                    // converted and stored; the accumulator is handed back to the MMA warp as soon
+                    // as the last chunk sits in registers.
+                    constexpr int kChunks = BN / 64;
+                    uint32_t v[2][2][32];
+                    ptx::tc_ld_32cols(t_acc, v[0][0]);
+                    ptx::tc_ld_32cols(t_acc + 32, v[0][1]);
+#pragma unroll
+                    for (int ci = 0; ci < kChunks; ++ci) {
                         ptx::tc_wait_ld();
+                        if (ci + 1 < kChunks) {
+                            ptx::tc_ld_32cols(t_acc + (ci + 1) * 64, v[(ci + 1) & 1][0]);
+                            ptx::tc_ld_32cols(t_acc + (ci + 1) * 64 + 32, v[(ci + 1) & 1][1]);
+                        } else {
+                            release_acc();
+                        }
                         // the buffer about to be overwritten was read by the store issued two chunks ago
                         if (lane == 0) ptx::bulk_wait_group_read<1>();
                         __syncwarp();
                         uint8_t* buf = staging_gen + store_buf * 4096 + lane * 128;
 #pragma unroll
                         for (int j = 0; j < 8; ++j)  // 16-byte pieces, 128-byte swizzle
-                            *reinterpret_cast<uint4*>(buf + ((j ^ (lane & 7)) << 4)) = pack8_fp16(&v[j >> 2][(j & 3) * 8]);
+                            *reinterpret_cast<uint4*>(buf + ((j ^ (lane & 7)) << 4)) = pack8_fp16(&v[ci & 1][j >> 2][(j & 3) * 8]);
                         ptx::fence_proxy_async_smem();
                         __syncwarp();
                         if (lane == 0 && mb * kBM + quad * 32 < p.M) {  // rows past M inside the box are clipped; one fixed lane owns the bulk groups
-                            ptx::tma_store_3d(&p.tma_c, staging + store_buf * 4096, nb * BN + c0, mb * kBM + quad * 32, l);
+                            ptx::tma_store_3d(&p.tma_c, staging + store_buf * 4096, nb * BN + ci * 64, mb * kBM + quad * 32, l);
                             ptx::bulk_commit_group();
                         }
                         store_buf ^= 1u;
@@ -500,8 +510,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                             for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(c_row + c0 + 8 * j) = pack8_fp16(&v[8 * j]);
                         }
                     }
+                    release_acc();
                 }
-                release_acc();
             } else {
                 // Partial tile: publish this worker's k-range as fp32 in its own slot.  Slot layout
                 // [BN/4][128 rows][4] keeps every warp-wide 16-byte access contiguous (512 bytes).

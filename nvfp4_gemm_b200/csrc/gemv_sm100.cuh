@@ -114,7 +114,7 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_nvfp4_kernel(const GemvPara
     for (int r = 0; r < R; ++r) sum[r] = 0.f;
 
     const int n_chunks = p.K / 64;
-    constexpr int UNROLL = (R == 1) ? 4 : 2;
+    constexpr int UNROLL = (R == 1) ? 4 : (R == 2 ? 2 : 1);
     for (int base = 0; base < n_chunks; base += 32 * UNROLL) {
         Chunk32 av[UNROLL][R];
         uint32_t sav[UNROLL][R];

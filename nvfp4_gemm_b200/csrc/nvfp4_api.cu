@@ -464,10 +464,13 @@ int nvfp4_gemv(const nvfp4_problem* p, void* stream_v) {
     g.c_row_stride = p->c_row_stride; g.c_batch_stride = p->c_batch_stride;
     g.M = p->m; g.K = p->k; g.L = p->l;
 
-    constexpr int R = 2;
-    const int rows_per_cta = kGemvWarps * R;
+    int r = 2;
+    if (const char* e = std::getenv("NVFP4_GEMV_R")) r = std::atoi(e);   // tuning knob
+    const int rows_per_cta = kGemvWarps * r;
     dim3 grid((p->m + rows_per_cta - 1) / rows_per_cta, p->l);
-    gemv_nvfp4_kernel<R><<<grid, kGemvThreads, 0, stream>>>(g);
+    if (r == 1) gemv_nvfp4_kernel<1><<<grid, kGemvThreads, 0, stream>>>(g);
+    else if (r == 4) gemv_nvfp4_kernel<4><<<grid, kGemvThreads, 0, stream>>>(g);
+    else gemv_nvfp4_kernel<2><<<grid, kGemvThreads, 0, stream>>>(g);
     CUDA_TRY(cudaGetLastError());
     g_launches.fetch_add(1);
     t_last_kernel = "gemv_warp_r2";

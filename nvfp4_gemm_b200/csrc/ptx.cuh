@@ -309,6 +309,11 @@ __device__ __forceinline__ float4 ld_cg_v4(const float* addr) {
 __device__ __forceinline__ void st_cg_v4(float* addr, float4 v) {
     asm volatile("st.global.cg.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
+__device__ __forceinline__ int ld_acquire_gpu(const int* addr) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+    return v;
+}
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
