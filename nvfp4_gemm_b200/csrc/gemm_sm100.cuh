@@ -77,11 +77,13 @@ struct GemmSmem {
     static constexpr uint32_t kSfaBytes = kMmaPerStage * kSfAtomBytes;
     static constexpr uint32_t kSfbBytes = (BN / 128) * kMmaPerStage * kSfAtomBytes;
     static constexpr uint32_t kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-    // Epilogue scratch: TMA-store staging (two 32-row x 128-byte buffers per warp) and the
-    // landing buffers of the partial-tile reduction share it; they are never live together.
+    // Epilogue scratch: TMA-store staging (two 32-row x 128-byte buffers per warp), or the landing
+    // area of the cluster split-K exchange.
     static constexpr uint32_t kEpiBytes = EPI_KB * 1024;
     static constexpr uint32_t kStagingPerWarp = 2 * 32 * 128;
-    static constexpr uint32_t kFixBufs = kEpiBytes / kFixChunkBytes;
+    // The finisher of a shared tile lands other workers' partials in the (then idle) operand ring.
+    static constexpr uint32_t kFixSlots = (STAGES * kStageBytes / kFixChunkBytes) < 12 ? (STAGES * kStageBytes / kFixChunkBytes) : 12;
+    static constexpr uint32_t kFixBufs = 12;  // barriers reserved for the landing slots
     static constexpr uint32_t kEpiOff = STAGES * kStageBytes;
     static constexpr uint32_t kBarOff = kEpiOff + kEpiBytes;
     static constexpr uint32_t kNumAcc = (BN <= 128) ? 2 : 1;
@@ -91,7 +93,7 @@ struct GemmSmem {
     static constexpr uint32_t kDynamicBytes = kBytes + 1024;  // slack for manual 1024-byte alignment
     static_assert(kStageBytes % 1024 == 0, "stage tiles must keep 1024-byte alignment");
     static_assert(!TMA_STORE || kEpiBytes >= 4 * kStagingPerWarp, "TMA-store staging does not fit");
-    static_assert(kFixBufs >= 2, "the partial-tile reduction needs at least two landing buffers");
+    static_assert(kFixSlots >= 2, "the partial-tile reduction needs at least two landing slots");
     static_assert(KS == 1 || (CG == 1 && BN / KS >= 32 && kEpiBytes >= kBM * BN * 4),
                   "cluster split-K: single-CTA MMAs, at least 32 columns per CTA, landing room for one fp32 tile");
     static_assert(kDynamicBytes <= 232448, "exceeds the 227 KB of shared memory one CTA may use");
@@ -150,7 +152,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
     const uint32_t tmem_slot = bar_fix_full + S::kFixBufs * 8;
     volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + S::kBarOff + S::kNumBars * 8);
     volatile uint32_t* abort_flag = tmem_slot_gen + 1;
-    volatile uint32_t* finisher_flag = tmem_slot_gen + 2;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -173,7 +174,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
             ptx::mbar_init(bar_acc_empty + a * 8, 128 * CG);
         }
         *abort_flag = 0u;
-        *finisher_flag = 0u;
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&p.tma_a);
         ptx::prefetch_tensormap(&p.tma_b);
@@ -378,7 +378,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
         const int epi_tid = threadIdx.x - 64;  // 0..127
         uint32_t acc_it = 0;
         uint32_t store_buf = 0;
-        uint32_t fix_it = 0;  // landing-buffer uses so far (buffer index and barrier parity)
+        uint32_t fix_parity = 0;  // phase parity of each landing-slot barrier
         for (int u = u_begin; u < u_end;) {
             const int tile = u / KT;
             const int k0 = u - tile * KT;
@@ -513,108 +513,114 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                     release_acc();
                 }
             } else {
-                // Partial tile: publish this worker's k-range as fp32 in its own slot.  Slot layout
-                // [BN/4][128 rows][4] keeps every warp-wide 16-byte access contiguous (512 bytes).
+                // Tile shared with other workers.  Whoever holds the START of the tile's k-range
+                // (its last piece of work: the tile continues in the next workers' ranges, which
+                // they process first) finishes the tile; everyone else publishes an fp32 partial.
+                const int w_first = unit_owner(tile * KT, n_workers, p.total_units);
+                int* counter = p.counters + w_first * CG + cta_rank;
 #ifdef NVFP4_TRACE
 #define NVFP4_MARK(i) if (epi_tid == 0) p.trace[blockIdx.x * 16 + (i)] = clock64() - trace_t_start
 #else
 #define NVFP4_MARK(i)
 #endif
                 NVFP4_MARK(8);
-                float* my_slot = p.scratch + static_cast<long long>(partial_slot(worker, k0, CG, cta_rank)) * (kBM * BN);
+                if (k0 > 0) {
+                    // Publish.  Slot layout [BN/4][128 rows][4] keeps every warp-wide 16-byte access
+                    // contiguous (512 bytes) and a 32-column chunk contiguous (16 KB).
+                    float* my_slot = p.scratch + static_cast<long long>(partial_slot(worker, k0, CG, cta_rank)) * (kBM * BN);
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 32) {
-                    uint32_t v[32];
-                    ptx::tc_ld_32cols(t_acc + c0, v);
-                    ptx::tc_wait_ld();
+                    for (int c0 = 0; c0 < BN; c0 += 32) {
+                        uint32_t v[32];
+                        ptx::tc_ld_32cols(t_acc + c0, v);
+                        ptx::tc_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        ptx::st_cg_v4(my_slot + ((c0 / 4 + j) * kBM + row_in_tile) * 4,
-                                      make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                                  __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
-                }
-                NVFP4_MARK(9);
-                release_acc();  // the MMA warp may start the next tile now
-                __threadfence();
-                NVFP4_MARK(10);
-                ptx::named_bar_sync(1, 128);
-                const int w_first = unit_owner(tile * KT, n_workers, p.total_units);
-                int* counter = p.counters + w_first * CG + cta_rank;
-                if (epi_tid == 0) {
-                    const int done = atomicAdd(counter, k1 - k0) + (k1 - k0);
-                    *finisher_flag = (done == KT) ? 1u : 0u;
-                }
-                ptx::named_bar_sync(1, 128);
-                const bool finisher = (*finisher_flag != 0u);
-                ptx::named_bar_sync(1, 128);  // the flag may be rewritten only after everyone read it
-                NVFP4_MARK(11);
-                if (finisher) {
-                    // Every contributor has published and fenced before bumping the counter.  Sum the
-                    // partials in ascending worker order, whoever the finisher is.
+                        for (int j = 0; j < 8; ++j)
+                            ptx::st_cg_v4(my_slot + ((c0 / 4 + j) * kBM + row_in_tile) * 4,
+                                          make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                      __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
+                    }
+                    release_acc();  // the MMA warp may start the next tile now
                     __threadfence();
-                    const int w_last = unit_owner(tile * KT + KT - 1, n_workers, p.total_units);
-                    // The partials are pulled into shared memory with bulk copies, kFixBufs chunks of
-                    // 32 columns (16 KB) in flight, and summed from there.
-                    if constexpr (TMA_STORE) {
-                        if (lane == 0) ptx::bulk_wait_group_read<0>();  // staging still read by earlier tile stores
-                    }
                     ptx::named_bar_sync(1, 128);
-                    // The first contributor started the tile (its "tail" slot); every later one joined
-                    // it from inside (its "head" slot), so no partition arithmetic is needed here.
-                    auto chunk_src = [&](int step, int n_contrib) -> const float* {
-                        const int i = step % n_contrib;
-                        const int slot = ((w_first + i) * 2 + (i == 0 ? 1 : 0)) * CG + cta_rank;
-                        return p.scratch + static_cast<long long>(slot) * (kBM * BN) +
-                               static_cast<long long>(step / n_contrib) * (kFixChunkBytes / 4);
-                    };
-                    const int n_contrib = w_last - w_first + 1;
-                    const int n_steps = (BN / 32) * n_contrib;
-                    const uint32_t fix_smem = smem_base + S::kEpiOff;
-                    const float* fix_gen = reinterpret_cast<const float*>(smem_gen + S::kEpiOff);
+                    if (epi_tid == 0) atomicAdd(counter, k1 - k0);
+                    NVFP4_MARK(9);
+                } else {
+                    // Finish: wait until the rest of the k-range has been published (normally long
+                    // ago), pull those partials into the now idle operand ring with bulk copies --
+                    // as many 16 KB chunks in flight as the ring holds -- and add them to this
+                    // worker's accumulator in ascending worker order.
+                    const int w_last = unit_owner(tile * KT + KT - 1, n_workers, p.total_units);
+                    const int n_others = w_last - w_first;
+                    const int need = KT - (k1 - k0);
+                    bool ready = true;
                     if (epi_tid == 0) {
-                        ptx::fence_proxy_async_all();  // other CTAs' plain stores -> this CTA's bulk reads
-                        for (int i = 0; i < static_cast<int>(S::kFixBufs) && i < n_steps; ++i) {
-                            const int bi = (fix_it + i) % S::kFixBufs;
-                            ptx::mbar_expect_tx(bar_fix_full + bi * 8, kFixChunkBytes);
-                            ptx::bulk_load(fix_smem + bi * kFixChunkBytes, chunk_src(i, n_contrib), kFixChunkBytes, bar_fix_full + bi * 8);
+                        const long long t_spin = clock64();
+                        while (ptx::ld_acquire_gpu(counter) < need) {
+                            if (*abort_flag || static_cast<uint64_t>(clock64() - t_spin) > timeout) {
+                                *abort_flag = 1u;
+                                ready = false;
+                                break;
+                            }
+                            __nanosleep(64);
                         }
+                        ptx::fence_proxy_async_all();  // other CTAs' plain stores -> this CTA's bulk reads
                     }
-                    NVFP4_MARK(12);
-                    float s[32];
+                    if constexpr (TMA_STORE) {
+                        if (lane == 0) ptx::bulk_wait_group<0>();  // earlier tile stores of this warp have left shared memory
+                    }
+                    if (!ptx::named_bar_and(1, 128, ready)) break;
+                    NVFP4_MARK(10);
+                    constexpr int kChunksPerTile = BN / 32;
+                    constexpr int kSlots = S::kFixSlots;
+                    const int n_chunks = kChunksPerTile * n_others;          // chunk q = (column chunk, contributor)
+                    const float* land_gen = reinterpret_cast<const float*>(smem_gen);
+                    auto issue = [&](int q) {
+                        const int ci = q / n_others, wi = q - ci * n_others;
+                        const int slot = ((w_first + 1 + wi) * 2) * CG + cta_rank;   // later contributors use their "head" slot
+                        const float* src = p.scratch + static_cast<long long>(slot) * (kBM * BN) + static_cast<long long>(ci) * (kFixChunkBytes / 4);
+                        const int b = q % kSlots;
+                        ptx::mbar_expect_tx(bar_fix_full + b * 8, kFixChunkBytes);
+                        ptx::bulk_load(smem_base + b * kFixChunkBytes, src, kFixChunkBytes, bar_fix_full + b * 8);
+                    };
+                    if (epi_tid == 0)
+                        for (int q = 0; q < n_chunks && q < kSlots; ++q) issue(q);
                     bool fix_ok = true;
 #pragma unroll 1
-                    for (int step = 0; step < n_steps; ++step) {
-                        const int b = (fix_it + step) % S::kFixBufs;
-                        const uint32_t par = ((fix_it + step) / S::kFixBufs) & 1u;
-                        fix_ok = ptx::mbar_wait_bounded(bar_fix_full + b * 8, par, abort_flag, timeout) && fix_ok;
-                        const float* src = fix_gen + b * (kFixChunkBytes / 4) + row_in_tile * 4;
-                        const bool first = (step % n_contrib) == 0;
+                    for (int ci = 0; ci < kChunksPerTile; ++ci) {
+                        uint32_t v[32];
+                        ptx::tc_ld_32cols(t_acc + ci * 32, v);
+                        ptx::tc_wait_ld();
+                        float s[32];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const float4 v = *reinterpret_cast<const float4*>(src + j * (kBM * 4));
-                            s[4 * j + 0] = (first ? 0.f : s[4 * j + 0]) + v.x;
-                            s[4 * j + 1] = (first ? 0.f : s[4 * j + 1]) + v.y;
-                            s[4 * j + 2] = (first ? 0.f : s[4 * j + 2]) + v.z;
-                            s[4 * j + 3] = (first ? 0.f : s[4 * j + 3]) + v.w;
-                        }
-                        if ((step % n_contrib) == n_contrib - 1 && row < p.M && fix_ok) {
-                            const int c0 = (step / n_contrib) * 32;
+                        for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(v[i]);
+#pragma unroll 1
+                        for (int wi = 0; wi < n_others; ++wi) {
+                            const int q = ci * n_others + wi;
+                            const int b = q % kSlots;
+                            fix_ok = ptx::mbar_wait_bounded(bar_fix_full + b * 8, (fix_parity >> b) & 1u, abort_flag, timeout) && fix_ok;
+                            fix_parity ^= (1u << b);
+                            const float* src = land_gen + b * (kFixChunkBytes / 4) + row_in_tile * 4;
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(c_row + c0 + 8 * j) = pack8_fp16(&s[8 * j]);
+                            for (int j = 0; j < 8; ++j) {
+                                const float4 t = *reinterpret_cast<const float4*>(src + j * (kBM * 4));
+                                s[4 * j] += t.x; s[4 * j + 1] += t.y; s[4 * j + 2] += t.z; s[4 * j + 3] += t.w;
+                            }
+                            if (q + kSlots < n_chunks) {          // the slot is needed again: refill once everyone has read it
+                                ptx::named_bar_sync(1, 128);
+                                if (epi_tid == 0) issue(q + kSlots);
+                            }
                         }
-                        ptx::named_bar_sync(1, 128);  // everyone is done with buffer b
-                        if (epi_tid == 0 && step + static_cast<int>(S::kFixBufs) < n_steps) {
-                            const int nxt = step + S::kFixBufs;
-                            ptx::mbar_expect_tx(bar_fix_full + b * 8, kFixChunkBytes);
-                            ptx::bulk_load(fix_smem + b * kFixChunkBytes, chunk_src(nxt, n_contrib), kFixChunkBytes, bar_fix_full + b * 8);
+                        if (row < p.M && fix_ok) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(c_row + ci * 32 + 8 * j) = pack8_fp16(&s[8 * j]);
                         }
                     }
-                    fix_it += n_steps;
+                    release_acc();
+                    if (epi_tid == 0) *counter = 0;
                     NVFP4_MARK(13);
 #ifdef NVFP4_TRACE
-                    if (epi_tid == 0) p.trace[blockIdx.x * 16 + 14] = n_steps;
+                    if (epi_tid == 0) p.trace[blockIdx.x * 16 + 14] = n_chunks;
 #endif
-                    if (epi_tid == 0) *counter = 0;
                 }
             }
             NVFP4_TRACE_END(trace_wait2);

@@ -371,11 +371,9 @@ int nvfp4_gemm(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* strea
     g.dbg_flags = std::getenv("NVFP4_DBG_FLAGS") ? std::atoi(std::getenv("NVFP4_DBG_FLAGS")) : 0;
 #endif
 
-    // TMA-store epilogue when whole tiles dominate (at least two tiles per worker); otherwise the
-    // deeper ring of the direct-store variant matters more than the store path.
+    // Whole tiles leave through the TMA-store epilogue unless the caller asks for plain stores.
     int epilogue = cf.epilogue;
-    const long long tiles = static_cast<long long>(g.tiles_m) * g.tiles_n * p->l;
-    if (epilogue == 0) epilogue = (tiles * cg >= 2LL * c->num_sms) ? 2 : 1;
+    if (epilogue == 0) epilogue = 2;
 
     const uint64_t kbytes = static_cast<uint64_t>(p->k) / 2;
     const uint64_t a_bs = p->l > 1 ? static_cast<uint64_t>(p->a_batch_stride) : static_cast<uint64_t>(p->a_row_stride) * p->m;
