@@ -85,6 +85,19 @@ int nvfp4_gemv(const nvfp4_problem* problem, void* stream);
 int nvfp4_matmul(const nvfp4_problem* problem, void* stream);
 
 /*
+ * GEMM fused with the all-gather of a column-parallel multi-GPU run: every finished piece of C is
+ * stored into this GPU's output and, at the same position, into n_peers (<= 7) other GPUs'
+ * outputs, so the transfer over NVLink overlaps the math tile by tile and no staging copy or
+ * re-layout pass is needed.  problem->c and c_peers[i] point at THIS rank's column block inside
+ * the full row-major output of each GPU (base + rank * n_local), problem->n is the local width and
+ * problem->c_row_stride the full width; c_peers[i] are peer-mapped device pointers (stores only;
+ * nothing is loaded from another GPU).  The caller synchronises the ranks after the kernel (all
+ * ranks' kernels must finish before any rank reads its output).  The reference has no multi-GPU
+ * code; no counterpart.
+ */
+int nvfp4_gemm_allgather(const nvfp4_problem* problem, void* const* c_peers, int n_peers, void* stream);
+
+/*
  * Column-parallel multi-GPU GEMM, last step: an all-gather of per-rank fp16 column blocks leaves
  * [blocks][rows][n_local] in memory; this writes the row-major [rows][blocks * n_local] matrix
  * (row stride dst_row_stride elements).  The reference has no multi-GPU code; no counterpart.

@@ -53,6 +53,11 @@ struct GemmParams {
     CUtensorMap tma_sfa; // permuted scales of A as {128 words, K/64 atoms, row blocks, L}, box {128, 4, 1, 1}
     CUtensorMap tma_sfb; // permuted scales of B, same view, box {128, 4, BN/128, 1}
     __half* c;
+    // Fused all-gather (column-parallel multi-GPU): every finished piece of C is also stored into
+    // the same position of n_peer other GPUs' output buffers (peer-mapped memory, stores only).
+    CUtensorMap tma_c_peer[7];
+    __half* c_peer[7];
+    int n_peer;
     float* scratch;      // partial-tile slots [worker][head|tail][cta of pair][BN/4][128][4] fp32
     int* counters;       // [worker][cta of pair] k-tiles published per shared tile; zero between launches
     int* status;         // host-visible status word
@@ -402,7 +407,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
             const uint32_t t_acc = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
             const bool whole_tile = (k1 - k0 == KT);
             const int row = mb * kBM + row_in_tile;
-            __half* c_row = p.c + l * p.c_batch_stride + static_cast<long long>(row) * p.c_row_stride + nb * BN;
+            const long long c_off = l * p.c_batch_stride + static_cast<long long>(row) * p.c_row_stride + nb * BN;
+            auto store8 = [&](int col, uint4 q) {  // eight fp16 of this thread's row, to the local C and every peer's
+                *reinterpret_cast<uint4*>(p.c + c_off + col) = q;
+                for (int r = 0; r < p.n_peer; ++r) *reinterpret_cast<uint4*>(p.c_peer[r] + c_off + col) = q;
+            };
             auto release_acc = [&]() {
                 ptx::tc_fence_before();
                 if (CG == 2 && !leader) ptx::mbar_arrive_cluster(bar_acc_empty + acc * 8, 0);
@@ -459,7 +468,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                     if (row < p.M) {
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
-                            *reinterpret_cast<uint4*>(c_row + ks_rank * kMyCols + c0 + 8 * j) = pack8_fp16(&s[8 * j]);
+                            store8(ks_rank * kMyCols + c0 + 8 * j, pack8_fp16(&s[8 * j]));
                     }
                 }
                 release_acc();
@@ -495,6 +504,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                         __syncwarp();
                         if (lane == 0 && mb * kBM + quad * 32 < p.M) {  // rows past M inside the box are clipped; one fixed lane owns the bulk groups
                             ptx::tma_store_3d(&p.tma_c, staging + store_buf * 4096, nb * BN + ci * 64, mb * kBM + quad * 32, l);
+                            for (int r = 0; r < p.n_peer; ++r)
+                                ptx::tma_store_3d(&p.tma_c_peer[r], staging + store_buf * 4096, nb * BN + ci * 64, mb * kBM + quad * 32, l);
                             ptx::bulk_commit_group();
                         }
                         store_buf ^= 1u;
@@ -507,7 +518,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                         ptx::tc_wait_ld();
                         if (row < p.M) {
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(c_row + c0 + 8 * j) = pack8_fp16(&v[8 * j]);
+                            for (int j = 0; j < 4; ++j) store8(c0 + 8 * j, pack8_fp16(&v[8 * j]));
                         }
                     }
                     release_acc();
@@ -612,7 +623,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                         }
                         if (row < p.M && fix_ok) {
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(c_row + ci * 32 + 8 * j) = pack8_fp16(&s[8 * j]);
+                            for (int j = 0; j < 4; ++j) store8(ci * 32 + 8 * j, pack8_fp16(&s[8 * j]));
                         }
                     }
                     release_acc();

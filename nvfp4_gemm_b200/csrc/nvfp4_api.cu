@@ -311,7 +311,10 @@ int validate_common(const nvfp4_problem* p) {
 
 extern "C" {
 
-int nvfp4_gemm(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* stream_v) {
+}  // extern "C"
+
+namespace {
+int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* const* c_peers, int n_peers, void* stream_v) {
     if (int rc = validate_common(p)) return rc;
     if (!p->sfa_perm || !p->sfb_perm)
         return fail(NVFP4_ERR_INVALID_ARGUMENT, "the GEMM needs the permuted scale tensors (sfa_perm, sfb_perm)");
@@ -385,10 +388,16 @@ int nvfp4_gemm(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* strea
                          &g.tma_b)) return rc;
     if (int rc = get_map(c, make_sf_key(p->sfa_perm, p->m, p->k, p->l, p->sfa_perm_batch_stride, 1), &g.tma_sfa)) return rc;
     if (int rc = get_map(c, make_sf_key(p->sfb_perm, p->n, p->k, p->l, p->sfb_perm_batch_stride, bn / 128), &g.tma_sfb)) return rc;
+    g.n_peer = n_peers;
+    for (int i = 0; i < n_peers; ++i) g.c_peer[i] = static_cast<__half*>(c_peers[i]);
     if (epilogue == 2) {
         if (int rc = get_map(c, make_key(p->c, p->n, p->m, p->l, static_cast<uint64_t>(p->c_row_stride) * 2, c_bs, 64, 32,
                                          CU_TENSOR_MAP_DATA_TYPE_FLOAT16),
                              &g.tma_c)) return rc;
+        for (int i = 0; i < n_peers; ++i)
+            if (int rc = get_map(c, make_key(c_peers[i], p->n, p->m, p->l, static_cast<uint64_t>(p->c_row_stride) * 2, c_bs, 64, 32,
+                                             CU_TENSOR_MAP_DATA_TYPE_FLOAT16),
+                                 &g.tma_c_peer[i])) return rc;
     }
 
     // Decode shapes (one 128-row block, fewer tiles than half the SMs): split K across a cluster
@@ -429,6 +438,27 @@ int nvfp4_gemm(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* strea
     if (bn == 128) return launch_gemm<1, 128, 4, false, 64>(c, 1, g, grid, stream, "gemm_1cta_n128_s4_direct");
     if (epilogue == 2) return launch_gemm<1, 256, 3, true, 32>(c, 2, g, grid, stream, "gemm_1cta_n256_s3_tmastore");
     return launch_gemm<1, 256, 3, false, 48>(c, 3, g, grid, stream, "gemm_1cta_n256_s3_direct");
+}
+}  // namespace
+
+extern "C" {
+
+int nvfp4_gemm(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* stream_v) {
+    return gemm_impl(p, cfg, nullptr, 0, stream_v);
+}
+
+int nvfp4_gemm_allgather(const nvfp4_problem* p, void* const* c_peers, int n_peers, void* stream_v) {
+    if (n_peers < 0 || n_peers > 7) return fail(NVFP4_ERR_INVALID_ARGUMENT, "n_peers must be between 0 and 7 (got %d)", n_peers);
+    if (n_peers > 0 && !c_peers) return fail(NVFP4_ERR_INVALID_ARGUMENT, "c_peers is NULL");
+    for (int i = 0; i < n_peers; ++i)
+        if (!c_peers[i] || !aligned(c_peers[i], 16)) return fail(NVFP4_ERR_INVALID_ARGUMENT, "c_peers[%d] must be a 16-byte aligned pointer", i);
+    if (p && p->m <= kBM && n_peers > 0) {
+        // decode shapes would take the cluster split-K kernel; keep them on the persistent kernel,
+        // whose epilogues all know about peers
+        nvfp4_gemm_config cf = {0, 0, 0, 0, 1};
+        return gemm_impl(p, &cf, c_peers, n_peers, stream_v);
+    }
+    return gemm_impl(p, nullptr, c_peers, n_peers, stream_v);
 }
 
 int nvfp4_gemv(const nvfp4_problem* p, void* stream_v) {

@@ -145,6 +145,50 @@ class ColumnParallelGemm:
         self.interleave_fn(self.gathered[idx], dst, p1 - p0, self.shard.n_local, self.world, c_full.stride(0))
 
 
+class FusedAllGatherGemm:
+    """Column-parallel GEMM whose epilogue is the all-gather: each rank's kernel stores every
+    finished tile of its column block into its own output AND into the same place of every peer's
+    output (peer-mapped symmetric memory, TMA / vector stores over NVLink).  No staging buffer, no
+    NCCL call, no re-layout pass; the transfer overlaps the math tile by tile.  Ranks are
+    synchronised before the kernel (nobody may still read the previous result) and after it
+    (everybody's stores have landed) with the symmetric-memory barrier, which is stream-ordered.
+    """
+
+    def __init__(self, m: int, n: int, k: int, group=None, device=None):
+        import ctypes
+        import os
+        # plain peer stores only: do not bind the buffer to an NVLink multicast object
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if self.world > 8:
+            raise ValueError("at most 8 GPUs (7 peers)")
+        self.shard = plan_shard(n, self.world, self.rank)
+        self.m, self.n, self.k = m, n, k
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.c_sym = symm_mem.empty((m * n,), dtype=torch.float16, device=self.device)
+        self.handle = symm_mem.rendezvous(self.c_sym, self.group)
+        self.c_full = self.c_sym.view(1, m, n).permute(1, 2, 0)            # [M, N, 1], row-major
+        col_off = self.shard.begin * 2                                      # bytes
+        peers = [int(self.handle.buffer_ptrs[r]) + col_off for r in range(self.world) if r != self.rank]
+        self.peer_array = (ctypes.c_void_p * max(1, len(peers)))(*peers)
+        self.n_peers = len(peers)
+
+    def __call__(self, local_data) -> torch.Tensor:
+        from . import _lib
+        from .submission import make_problem
+        lib = _lib.load()
+        c_block = self.c_full[:, self.shard.begin:self.shard.end]          # this rank's columns, row stride N
+        problem = make_problem(tuple(local_data[:6]) + (c_block,))
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        self.handle.barrier(channel=0)
+        _lib.check(lib.nvfp4_gemm_allgather(problem, self.peer_array, self.n_peers, stream))
+        self.handle.barrier(channel=1)
+        return self.c_full
+
+
 def bench_column_parallel(args, w, rank, world, dev, ClockSampler, measured_peaks, algorithmic_flops):
     """`bench.py --gpus N` for N > 1: strong scaling of the one partitioned workload."""
     import json
@@ -161,11 +205,24 @@ def bench_column_parallel(args, w, rank, world, dev, ClockSampler, measured_peak
         local = shard_inputs(full, shard)
         sets.append(tuple(to_device_same_layout(t, dev) if j < 6 else None for j, t in enumerate(local)))
         del full
-    c_full = [torch.empty((1, m, n), dtype=torch.float16, device=dev).permute(1, 2, 0) for _ in range(n_sets)]
-    plan = ColumnParallelGemm(m, n, k, device=dev, panels=4)
+    mode = getattr(args, "allgather", "fused")
+    fused = None
+    if mode == "fused":
+        try:
+            fused = FusedAllGatherGemm(m, n, k, device=dev)
+        except Exception as e:  # symmetric memory unavailable on this box: use the NCCL path and say so
+            mode = f"nccl (fused path unavailable: {str(e)[:120]})"
+    if fused is not None:
+        c_full = [fused.c_full]
 
-    def step(i):
-        plan(sets[i % n_sets], c_full[i % n_sets])
+        def step(i):
+            fused(sets[i % n_sets])
+    else:
+        c_full = [torch.empty((1, m, n), dtype=torch.float16, device=dev).permute(1, 2, 0)]
+        plan = ColumnParallelGemm(m, n, k, device=dev, panels=4)
+
+        def step(i):
+            plan(sets[i % n_sets], c_full[0])
 
     for i in range(args.warmup):
         step(i)
@@ -210,7 +267,8 @@ def bench_column_parallel(args, w, rank, world, dev, ClockSampler, measured_peak
     # GEMM-only time of this rank's block, for the split of compute vs exchange
     torch.cuda.synchronize()
     g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    local = sets[0][:6] + (plan.staging.permute(1, 2, 0),)
+    gemm_only_c = torch.empty((1, m, shard.n_local), dtype=torch.float16, device=dev).permute(1, 2, 0)
+    local = sets[0][:6] + (gemm_only_c,)
     S.custom_kernel(local)
     g0.record()
     for _ in range(5):
@@ -228,7 +286,9 @@ def bench_column_parallel(args, w, rank, world, dev, ClockSampler, measured_peak
         line = dict(metric="nvfp4_matmul_throughput", value=tflops, unit="TFLOP/s", n_gpus=world, steps=args.steps,
                     warmup=args.warmup, ms_per_step=ms_per_step, higher_is_better=True, scaling="strong", vs_baseline=None,
                     dtype="e2m1 x ue4m3 -> f32 -> f16", data="synthetic",
-                    config=dict(workload=w["name"], parallelism=f"column-parallel over N on {world} GPUs, NCCL all-gather of fp16 blocks, 4 row panels",
+                    config=dict(workload=w["name"], parallelism=(f"column-parallel over N on {world} GPUs; all-gather fused into the GEMM epilogue (peer stores over NVLink)"
+                                             if fused is not None else
+                                             f"column-parallel over N on {world} GPUs, NCCL all-gather of fp16 blocks, 4 row panels, {mode}"),
                                 timing="CUDA events, max over ranks; 2 rotating input sets (302 MB per rank set) > L2",
                                 gemm_only_ms_per_rank=float(gemm_ms.item()),
                                 gemm_only_tflops_per_gpu=flops / world / (float(gemm_ms.item()) * 1e-3) / 1e12,
