@@ -115,6 +115,17 @@ int nvfp4_permute_scales(const void* plain, void* permuted, int32_t rows, int32_
                          int64_t plain_batch_stride, int64_t permuted_batch_stride, void* stream);
 
 /*
+ * NVFP4 quantiser, the step that produces the operator's inputs: fp16 (x_is_bf16 = 0) or bf16
+ * [rows][k] -> packed e2m1 [rows][k/2] plus one e4m3 scale per 16 elements, written in the plain
+ * layout (sf_plain, may be NULL) and / or the permuted atom layout (sf_permuted, may be NULL;
+ * ceil(rows/128) * (k/64) * 512 bytes).  scale = RN-even, saturating e4m3 of max|x|/6; element =
+ * RN-even, saturating e2m1 of x/scale.  x_row_stride in elements, the others in bytes.  The
+ * reference receives already-quantised tensors from its harness (template.py:9-15); no counterpart.
+ */
+int nvfp4_quantize(const void* x, int32_t x_is_bf16, void* packed, void* sf_plain, void* sf_permuted, int32_t rows, int32_t k,
+                   int64_t x_row_stride, int64_t packed_row_stride, int64_t sf_plain_row_stride, void* stream);
+
+/*
  * The same GEMM for callers that cannot allocate device memory when they call: code that runs
  * while another thread captures a CUDA graph in global capture mode (cudaMalloc is illegal
  * then), services that hand all free HBM to their own pool at start-up so that a later

@@ -4,6 +4,8 @@
 //   * permute_scales: plain [rows][K/16] scale bytes -> the 512-byte atom layout the tensor-core
 //     GEMM reads (ref.txt:31, s_128t.py:554-562 in the reference project).
 #pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -53,6 +55,66 @@ __global__ void __launch_bounds__(256) permute_scales_kernel(const uint8_t* __re
         }
         *reinterpret_cast<uint4*>(perm + l * perm_batch_stride + (static_cast<long long>(rb) * atoms_k + kk) * 512 + r32 * 16) =
             make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+// NVFP4 quantiser (the step before the matmul): fp16 / bf16 [rows][K] -> packed e2m1 + one e4m3
+// scale per 16 elements, scale = RN(max|x| / 6), element = RN(x / scale) saturated to +-6.  One
+// thread owns one 16-element block: 32 bytes in, 8 bytes + one scale byte out (plain layout and /
+// or the permuted 128 x 4 atom layout).
+template <bool BF16>
+__global__ void __launch_bounds__(256) quantize_nvfp4_kernel(const void* __restrict__ x, uint8_t* __restrict__ packed,
+                                                             uint8_t* __restrict__ sf_plain, uint8_t* __restrict__ sf_perm, int rows,
+                                                             int k, long long x_row_stride, long long packed_row_stride,
+                                                             long long sf_plain_row_stride) {
+    const int blocks_per_row = k / 16;
+    const long long total = static_cast<long long>(rows) * blocks_per_row;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int row = static_cast<int>(i / blocks_per_row);
+        const int blk = static_cast<int>(i - static_cast<long long>(row) * blocks_per_row);
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + row * x_row_stride + blk * 16);
+        const uint4 lo = __ldcs(src), hi = __ldcs(src + 1);
+        const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (BF16) {
+                v[2 * j] = __uint_as_float(w[j] << 16);
+                v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+            } else {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+                v[2 * j] = f.x;
+                v[2 * j + 1] = f.y;
+            }
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
+        // scale byte: round-to-nearest-even, saturating e4m3 of amax / 6
+        uint16_t sf_pair;
+        const float want = __fdiv_rn(amax, 6.0f);
+        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(sf_pair) : "f"(0.0f), "f"(want));
+        const uint8_t sf_byte = static_cast<uint8_t>(sf_pair & 0xff);
+        uint32_t sf_h2;
+        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(sf_h2) : "h"(sf_pair));
+        const float scale = __low2float(*reinterpret_cast<__half2*>(&sf_h2));
+        uint32_t out[2] = {0u, 0u};
+        if (scale > 0.f) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float a = __fdiv_rn(v[2 * j], scale), b = __fdiv_rn(v[2 * j + 1], scale);
+                uint32_t byte;
+                asm("{\n\t.reg .b8 q;\n\tcvt.rn.satfinite.e2m1x2.f32 q, %1, %2;\n\tcvt.u32.u8 %0, q;\n\t}" : "=r"(byte) : "f"(b), "f"(a));
+                out[j >> 2] |= byte << (8 * (j & 3));
+            }
+        }
+        *reinterpret_cast<uint2*>(packed + row * packed_row_stride + blk * 8) = make_uint2(out[0], out[1]);
+        if (sf_plain) sf_plain[row * sf_plain_row_stride + blk] = sf_byte;
+        if (sf_perm) {
+            const long long off = (static_cast<long long>(row / 128) * (k / 64) + blk / 4) * 512 + (row % 32) * 16 + ((row / 32) % 4) * 4 + (blk % 4);
+            sf_perm[off] = sf_byte;
+        }
     }
 }
 

@@ -549,6 +549,42 @@ int nvfp4_permute_scales(const void* plain, void* permuted, int32_t rows, int32_
     return NVFP4_OK;
 }
 
+int nvfp4_quantize(const void* x, int32_t x_is_bf16, void* packed, void* sf_plain, void* sf_permuted, int32_t rows, int32_t k,
+                   int64_t x_row_stride, int64_t packed_row_stride, int64_t sf_plain_row_stride, void* stream_v) {
+    if (!x || !packed) return fail(NVFP4_ERR_INVALID_ARGUMENT, "x and packed must not be NULL");
+    if (!sf_plain && !sf_permuted) return fail(NVFP4_ERR_INVALID_ARGUMENT, "at least one of sf_plain / sf_permuted is needed");
+    if (rows < 1 || k < 64 || k % 64) return fail(NVFP4_ERR_INVALID_ARGUMENT, "rows >= 1 and k a positive multiple of 64 required");
+    if (!aligned(x, 16) || x_row_stride % 8 || x_row_stride < k)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "x must be 16-byte aligned with a row stride (elements) that is a multiple of 8 and >= k");
+    if (!aligned(packed, 8) || packed_row_stride % 8 || packed_row_stride < k / 2)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "packed must be 8-byte aligned with a row stride that is a multiple of 8 and >= k/2");
+    if (sf_plain && sf_plain_row_stride < k / 16) return fail(NVFP4_ERR_INVALID_ARGUMENT, "sf_plain_row_stride must be >= k/16");
+    int dev = 0, sms = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const long long total = static_cast<long long>(rows) * (k / 16);
+    long long grid = (total + 255) / 256;
+    if (grid > static_cast<long long>(sms) * 16) grid = static_cast<long long>(sms) * 16;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    if (sf_permuted && rows % 128) {
+        // rows of the last 128-row block that do not exist must read as zero scales
+        const long long bytes = static_cast<long long>((rows + 127) / 128) * (k / 64) * 512;
+        const long long tail = static_cast<long long>(k / 64) * 512;
+        CUDA_TRY(cudaMemsetAsync(static_cast<uint8_t*>(sf_permuted) + bytes - tail, 0, tail, stream));
+    }
+    if (x_is_bf16)
+        quantize_nvfp4_kernel<true><<<static_cast<int>(grid), 256, 0, stream>>>(x, static_cast<uint8_t*>(packed), static_cast<uint8_t*>(sf_plain),
+                                                                               static_cast<uint8_t*>(sf_permuted), rows, k, x_row_stride,
+                                                                               packed_row_stride, sf_plain_row_stride);
+    else
+        quantize_nvfp4_kernel<false><<<static_cast<int>(grid), 256, 0, stream>>>(x, static_cast<uint8_t*>(packed), static_cast<uint8_t*>(sf_plain),
+                                                                                static_cast<uint8_t*>(sf_permuted), rows, k, x_row_stride,
+                                                                                packed_row_stride, sf_plain_row_stride);
+    CUDA_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    return NVFP4_OK;
+}
+
 int nvfp4_matmul(const nvfp4_problem* p, void* stream) {
     if (p && p->n == 1) return nvfp4_gemv(p, stream);
     return nvfp4_gemm(p, nullptr, stream);

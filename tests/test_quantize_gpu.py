@@ -1,0 +1,68 @@
+"""GPU parity of the NVFP4 quantiser (the producer of the operator's inputs) against the oracle's
+statement of it, and a round trip through the GEMM."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def cuda_lib(lib):
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    return lib
+
+
+def _quantize(cuda_lib, x):
+    from nvfp4_gemm_b200 import _lib
+    rows, k = x.shape
+    packed = torch.empty((rows, k // 2), dtype=torch.uint8, device="cuda")
+    sf = torch.empty((rows, k // 16), dtype=torch.uint8, device="cuda")
+    perm = torch.full((((rows + 127) // 128) * (k // 64) * 512,), 0xEE, dtype=torch.uint8, device="cuda")
+    _lib.check(cuda_lib.nvfp4_quantize(x.data_ptr(), int(x.dtype == torch.bfloat16), packed.data_ptr(), sf.data_ptr(), perm.data_ptr(),
+                                       rows, k, x.stride(0), k // 2, k // 16, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    return packed, sf, perm
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,k", [(128, 256), (300, 1024), (1, 64), (4096, 7168)])
+def test_quantizer_matches_oracle_bit_for_bit(cuda_lib, oracle, dtype, rows, k):
+    g = torch.Generator().manual_seed(rows + k)
+    x = (torch.randn((rows, k), generator=g) * torch.exp(torch.randn((rows, 1), generator=g))).to(dtype)
+    x[0, :16] = 0                                   # an all-zero block
+    x[-1, -16:] = 1000.0 if dtype == torch.float16 else 1e6   # saturating scale / elements
+    packed, sf, perm = _quantize(cuda_lib, x.cuda())
+    exp_packed, exp_sf = oracle.quantize_rows(x.float().numpy())
+    assert np.array_equal(sf.cpu().numpy(), exp_sf)
+    assert np.array_equal(packed.cpu().numpy(), exp_packed)
+    assert np.array_equal(perm.cpu().numpy(), oracle.permute_sf(exp_sf[:, :, None]))
+
+
+def test_quantize_then_gemm_approximates_the_fp32_product(cuda_lib, oracle):
+    from nvfp4_gemm_b200 import submission
+    from nvfp4_gemm_b200.inputs import FP4_DTYPE, SF_DTYPE
+    m, n, k = 256, 512, 2048
+    g = torch.Generator().manual_seed(0)
+    a = torch.randn((m, k), generator=g).half().cuda()
+    b = torch.randn((n, k), generator=g).half().cuda()
+    pa, sa, ppa = _quantize(cuda_lib, a)
+    pb, sb, ppb = _quantize(cuda_lib, b)
+    c = torch.empty((1, m, n), dtype=torch.float16, device="cuda").permute(1, 2, 0)
+
+    def perm_view(p, rows):
+        return p.view(1, (rows + 127) // 128, k // 64, 32, 4, 4).permute(3, 4, 1, 5, 2, 0).view(SF_DTYPE)
+
+    data = (pa.view(1, m, k // 2).permute(1, 2, 0).view(FP4_DTYPE), pb.view(1, n, k // 2).permute(1, 2, 0).view(FP4_DTYPE),
+            sa.view(1, m, k // 16).permute(1, 2, 0).view(SF_DTYPE), sb.view(1, n, k // 16).permute(1, 2, 0).view(SF_DTYPE),
+            perm_view(ppa, m), perm_view(ppb, n), c)
+    out = submission.custom_kernel(data)
+    submission.check_status()
+    # exact against the oracle on the quantised operands ...
+    exp = oracle.ref_gemm(pa.cpu().numpy()[:, :, None], pb.cpu().numpy()[:, :, None], sa.cpu().numpy()[:, :, None], sb.cpu().numpy()[:, :, None], accumulate="f64")
+    np.testing.assert_allclose(out.cpu().numpy().astype(np.float32), exp.astype(np.float32), rtol=1e-3, atol=1e-3)
+    # ... and close to the unquantised product (4-bit operands: a few percent of the output scale)
+    ref = (a.float() @ b.float().t()).cpu().numpy()
+    err = np.abs(out[:, :, 0].float().cpu().numpy() - ref)
+    assert err.mean() < 0.12 * np.abs(ref).mean() + 0.5
