@@ -477,29 +477,39 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                     // 64 columns (128 bytes of fp16) at a time through a swizzled 32-row staging buffer.
                     uint8_t* staging_gen = smem_gen + S::kEpiOff + (warp - 2) * S::kStagingPerWarp;
                     const uint32_t staging = smem_base + S::kEpiOff + (warp - 2) * S::kStagingPerWarp;
-                    // Software-pipelined: the TMEM loads of chunk i+1 are in flight while chunk i is
-                    // converted and stored; the accumulator is handed back to the MMA warp as soon
-                    // as the last chunk sits in registers.
-                    constexpr int kChunks = BN / 64;
-                    uint32_t v[2][2][32];
-                    ptx::tc_ld_32cols(t_acc, v[0][0]);
-                    ptx::tc_ld_32cols(t_acc + 32, v[0][1]);
+                    // Phase 1, drain: the whole accumulator row of this thread goes TMEM -> registers
+                    // -> fp16 pairs (BN/2 registers), the loads of the next 32 columns in flight while
+                    // the previous ones are converted.  The accumulator is handed back to the MMA warp
+                    // as soon as the last column is in registers, before anything is stored: the TMA
+                    // stores queue behind the producer's loads in the same TMA unit and are slow to
+                    // free their staging buffer.
+                    constexpr int kLoads = BN / 32;
+                    uint32_t packed[BN / 2];
+                    uint32_t v[2][32];
+                    ptx::tc_ld_32cols(t_acc, v[0]);
 #pragma unroll
-                    for (int ci = 0; ci < kChunks; ++ci) {
+                    for (int ci = 0; ci < kLoads; ++ci) {
                         ptx::tc_wait_ld();
-                        if (ci + 1 < kChunks) {
-                            ptx::tc_ld_32cols(t_acc + (ci + 1) * 64, v[(ci + 1) & 1][0]);
-                            ptx::tc_ld_32cols(t_acc + (ci + 1) * 64 + 32, v[(ci + 1) & 1][1]);
-                        } else {
-                            release_acc();
+                        if (ci + 1 < kLoads) ptx::tc_ld_32cols(t_acc + (ci + 1) * 32, v[(ci + 1) & 1]);
+                        else release_acc();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const __half2 h = __floats2half2_rn(__uint_as_float(v[ci & 1][2 * j]), __uint_as_float(v[ci & 1][2 * j + 1]));
+                            packed[ci * 16 + j] = *reinterpret_cast<const uint32_t*>(&h);
                         }
+                    }
+                    // Phase 2, store: 64 columns (128 bytes of fp16) at a time through the swizzled
+                    // 32-row staging buffers, overlapping the next tile's MMAs.
+#pragma unroll
+                    for (int ci = 0; ci < BN / 64; ++ci) {
                         // the buffer about to be overwritten was read by the store issued two chunks ago
                         if (lane == 0) ptx::bulk_wait_group_read<1>();
                         __syncwarp();
                         uint8_t* buf = staging_gen + store_buf * 4096 + lane * 128;
 #pragma unroll
                         for (int j = 0; j < 8; ++j)  // 16-byte pieces, 128-byte swizzle
-                            *reinterpret_cast<uint4*>(buf + ((j ^ (lane & 7)) << 4)) = pack8_fp16(&v[ci & 1][j >> 2][(j & 3) * 8]);
+                            *reinterpret_cast<uint4*>(buf + ((j ^ (lane & 7)) << 4)) =
+                                make_uint4(packed[ci * 32 + 4 * j], packed[ci * 32 + 4 * j + 1], packed[ci * 32 + 4 * j + 2], packed[ci * 32 + 4 * j + 3]);
                         ptx::fence_proxy_async_smem();
                         __syncwarp();
                         if (lane == 0 && mb * kBM + quad * 32 < p.M) {  // rows past M inside the box are clipped; one fixed lane owns the bulk groups
