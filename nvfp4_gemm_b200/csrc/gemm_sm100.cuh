@@ -99,8 +99,8 @@ struct GemmSmem {
     static_assert(kStageBytes % 1024 == 0, "stage tiles must keep 1024-byte alignment");
     static_assert(!TMA_STORE || kEpiBytes >= 4 * kStagingPerWarp, "TMA-store staging does not fit");
     static_assert(kFixSlots >= 2, "the partial-tile reduction needs at least two landing slots");
-    static_assert(KS == 1 || (CG == 1 && BN / KS >= 32 && kEpiBytes >= kBM * BN * 4),
-                  "cluster split-K: single-CTA MMAs, at least 32 columns per CTA, landing room for one fp32 tile");
+    static_assert(KS == 1 || (CG == 1 && BN / KS >= 32 && STAGES * kStageBytes >= kBM * BN * 4),
+                  "cluster split-K: single-CTA MMAs, at least 32 columns per CTA, the ring must hold one fp32 tile");
     static_assert(kDynamicBytes <= 232448, "exceeds the 227 KB of shared memory one CTA may use");
 };
 
@@ -166,14 +166,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
     // 1/KS of K with its own MMAs and TMEM; the partial sums are exchanged through distributed
     // shared memory and every CTA finalises BN/KS columns.
     const int ks_rank = (KS > 1) ? static_cast<int>(ptx::cluster_ctarank()) : 0;
-    const uint32_t bar_land = bar_fix_full;  // KS > 1: "all peers' partial columns have landed"
+    const uint32_t bar_land = bar_fix_full;       // KS > 1: "all peers' partial columns have landed"
+    const uint32_t bar_ready = bar_fix_full + 8;  // KS > 1: "all peers are done with their operand ring"
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             ptx::mbar_init(bar_full + s * 8, 1);
             ptx::mbar_init(bar_empty + s * 8, 1);
         }
-        for (uint32_t b = 0; b < S::kFixBufs; ++b) ptx::mbar_init(bar_fix_full + b * 8, (KS > 1 && b == 0) ? 128 * (KS - 1) : 1);
+        for (uint32_t b = 0; b < S::kFixBufs; ++b)
+            ptx::mbar_init(bar_fix_full + b * 8, (KS > 1 && b == 0) ? 128 * (KS - 1) : (KS > 1 && b == 1) ? (KS - 1) : 1);
         for (int a = 0; a < 2; ++a) {
             ptx::mbar_init(bar_acc_full + a * 8, 1);
             ptx::mbar_init(bar_acc_empty + a * 8, 128 * CG);
@@ -186,21 +188,31 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
         ptx::prefetch_tensormap(&p.tma_sfb);
         if (TMA_STORE) ptx::prefetch_tensormap(&p.tma_c);
     }
-    if constexpr (CG == 2 || KS > 1) {
-        // every CTA of the cluster is resident and has initialised its barriers before any
-        // pair-wide instruction or remote arrival is issued
-        __syncthreads();
+    __syncthreads();  // barriers initialised
+    bool cluster_waited = true;
+    if constexpr (CG == 2) {
+        // both CTAs of the pair are resident and have initialised their barriers before the first
+        // load signals the leader's barrier or any pair-wide instruction is issued
         ptx::cluster_arrive();
         ptx::cluster_wait();
+    } else if constexpr (KS > 1) {
+        // split-K peers touch this CTA only in the exchange epilogue: arrive now, wait there
+        ptx::cluster_arrive();
+        cluster_waited = false;
     }
+    // TMEM is allocated by warp 1 while warp 0 already streams operands; warps 1..5 meet on a
+    // named barrier to pick up the base address.
+    uint32_t tmem_base = 0;
     if (warp == 1) {
         ptx::tmem_alloc<CG>(tmem_slot, kTmemCols);
         ptx::tmem_relinquish<CG>();
+        ptx::tc_fence_before();
     }
-    ptx::tc_fence_before();
-    __syncthreads();
-    ptx::tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot_gen;
+    if (warp != 0) {
+        ptx::named_bar_sync(3, kGemmThreads - 32);
+        ptx::tc_fence_after();
+        tmem_base = *tmem_slot_gen;
+    }
 
     const int KT = p.k_tiles;
     const int n_workers = (KS > 1) ? static_cast<int>(gridDim.x) : static_cast<int>(gridDim.x) / CG;
@@ -421,9 +433,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
             if constexpr (KS > 1) {
                 constexpr int kMyCols = BN / KS;                     // columns this CTA finalises
                 constexpr uint32_t kPieceBytes = kMyCols * kBM * 4;  // one sender's columns, [col/4][128 rows][4]
-                const uint32_t land = smem_base + S::kEpiOff;
-                const float* land_gen = reinterpret_cast<const float*>(smem_gen + S::kEpiOff);
-                // 1. send every peer the columns it finalises
+                // The partial sums land in the operand ring, which is idle once a CTA's own MMAs
+                // are done (the accumulator is ready): every CTA tells its peers so, and nobody
+                // sends before all peers have said it.
+                const uint32_t land = smem_base;
+                const float* land_gen = reinterpret_cast<const float*>(smem_gen);
+                if (!cluster_waited) { ptx::cluster_wait(); cluster_waited = true; }
+                if (epi_tid == 0) {
+                    for (int q = 0; q < KS; ++q)
+                        if (q != ks_rank) ptx::mbar_arrive_cluster(bar_ready, q);
+                }
+                const bool peers_ready = ptx::mbar_wait_bounded<true>(bar_ready, 0u, abort_flag, timeout);
+                if (!ptx::named_bar_and(2, 128, peers_ready)) break;
+                // 1. send every peer the columns it finalises (peers are resident and initialised)
+                if (!cluster_waited) { ptx::cluster_wait(); cluster_waited = true; }
 #pragma unroll 1
                 for (int q = 0; q < KS; ++q) {
                     if (q == ks_rank) continue;
@@ -661,6 +684,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
     }
 
     // ---------------------------------------------------------------- teardown
+    if (!cluster_waited) ptx::cluster_wait();  // the start-up cluster phase, for warps that had no reason to wait earlier
     ptx::tc_fence_before();
     __syncthreads();
     if (*abort_flag) {

@@ -336,8 +336,8 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* const*
         return fail(NVFP4_ERR_INVALID_ARGUMENT, "tile_n must be 0, 128 or 256");
     if (cf.epilogue < 0 || cf.epilogue > 2) return fail(NVFP4_ERR_INVALID_ARGUMENT, "epilogue must be 0, 1 or 2");
     if (cf.cta_group < 0 || cf.cta_group > 2) return fail(NVFP4_ERR_INVALID_ARGUMENT, "cta_group must be 0, 1 or 2");
-    if (cf.split_k != 0 && cf.split_k != 1 && cf.split_k != 2 && cf.split_k != 4)
-        return fail(NVFP4_ERR_INVALID_ARGUMENT, "split_k must be 0, 1, 2 or 4");
+    if (cf.split_k != 0 && cf.split_k != 1 && cf.split_k != 2 && cf.split_k != 4 && cf.split_k != 8)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "split_k must be 0, 1, 2, 4 or 8");
 
     DeviceCtx* c = nullptr;
     if (int rc = get_ctx(&c)) return rc;
@@ -406,25 +406,32 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* const*
     if (ks == 0) {
         ks = 1;
         const long long tiles128 = static_cast<long long>(p->n / 128) * p->l;
-        if (p->m <= kBM && cf.cta_group != 2 && (cf.tile_n == 0 || cf.tile_n == 128) && cf.grid == 0) {
-            if (tiles128 * 4 <= c->num_sms && g.k_tiles >= 8) ks = 4;
+        if (p->m <= kBM && cf.cta_group != 2 && cf.tile_n == 0 && cf.grid == 0) {
+            // measured: two CTAs per tile beat four whenever both fit in one wave (the exchange
+            // grows with the cluster); four only pays when there are very few tiles
+            if (tiles128 * 4 <= c->num_sms / 2 && g.k_tiles >= 16) ks = 4;
             else if (tiles128 * 2 <= c->num_sms && g.k_tiles >= 4) ks = 2;
         }
     }
     if (ks > 1) {
         if (cf.cta_group == 2) return fail(NVFP4_ERR_INVALID_ARGUMENT, "split_k > 1 uses single-CTA tiles (cta_group 1)");
-        if (bn != 128 && cf.tile_n != 0) return fail(NVFP4_ERR_INVALID_ARGUMENT, "split_k > 1 needs tile_n 128");
         if (g.k_tiles < ks) return fail(NVFP4_ERR_INVALID_ARGUMENT, "split_k = %d needs k >= %d", ks, ks * kKPerStage);
-        // plan for single-CTA 128 x 128 tiles, whatever the stream-K planning above chose
-        bn = 128;
+        // single-CTA tiles of 128 x bn_ks, whatever the stream-K planning above chose
+        int bn_ks = cf.tile_n ? cf.tile_n : 128;
+        if (ks == 8) bn_ks = 256;                      // 32 columns per CTA at least
+        if (ks == 2 && bn_ks == 256) return fail(NVFP4_ERR_INVALID_ARGUMENT, "split_k = 2 is built for tile_n 128");
+        if (p->n % bn_ks) return fail(NVFP4_ERR_INVALID_ARGUMENT, "n = %d is not a multiple of tile_n = %d", p->n, bn_ks);
+        bn = bn_ks;
         g.tiles_m = (p->m + kBM - 1) / kBM;
         g.tiles_n = p->n / bn;
         g.total_units = g.tiles_m * g.tiles_n * p->l * g.k_tiles;
         if (int rc = get_map(c, make_key(p->b, kbytes, p->n, p->l, p->b_row_stride, b_bs, kBKBytes, bn, CU_TENSOR_MAP_DATA_TYPE_UINT8),
                              &g.tma_b)) return rc;
-        if (int rc = get_map(c, make_sf_key(p->sfb_perm, p->n, p->k, p->l, p->sfb_perm_batch_stride, 1), &g.tma_sfb)) return rc;
-        if (ks == 2) return launch_gemm_splitk<128, 4, 64, 2>(c, 8, g, stream, "gemm_splitk2_n128_s4");
-        return launch_gemm_splitk<128, 4, 64, 4>(c, 9, g, stream, "gemm_splitk4_n128_s4");
+        if (int rc = get_map(c, make_sf_key(p->sfb_perm, p->n, p->k, p->l, p->sfb_perm_batch_stride, bn / 128), &g.tma_sfb)) return rc;
+        if (bn == 128 && ks == 2) return launch_gemm_splitk<128, 6, 0, 2>(c, 8, g, stream, "gemm_splitk2_n128_s6");
+        if (bn == 128) return launch_gemm_splitk<128, 6, 0, 4>(c, 9, g, stream, "gemm_splitk4_n128_s6");
+        if (ks == 4) return launch_gemm_splitk<256, 4, 0, 4>(c, 10, g, stream, "gemm_splitk4_n256_s4");
+        return launch_gemm_splitk<256, 4, 0, 8>(c, 11, g, stream, "gemm_splitk8_n256_s4");
     }
 
     const int grid = cf.grid;

@@ -63,15 +63,15 @@ def test_every_kernel_variant_and_split_pattern(sub, oracle, variant, shape, gri
     assert_bit_exact(data[6], expected_fp16(oracle, data), what=f"second launch {shape}")
 
 
-@pytest.mark.parametrize("split_k", [2, 4])
-@pytest.mark.parametrize("shape", [(128, 256, 2048, 1), (77, 384, 2304, 2), (128, 512, 1024, 1), (1, 128, 1280, 1), (200, 256, 2048, 1)])
-def test_cluster_split_k(sub, oracle, split_k, shape):
+@pytest.mark.parametrize("split_k,tile_n", [(2, 0), (4, 0), (4, 256), (8, 0)])
+@pytest.mark.parametrize("shape", [(128, 256, 2048, 1), (77, 512, 2304, 2), (128, 512, 2048, 1), (1, 256, 2048, 1), (200, 256, 2048, 1)])
+def test_cluster_split_k(sub, oracle, split_k, tile_n, shape):
     """K split across a cluster, partial sums exchanged through distributed shared memory."""
     from nvfp4_gemm_b200.inputs import generate_input
     m, n, k, l = shape
     data = generate_input(m, n, k, l, 21)
     data[6].view(torch.int16).fill_(0x7fff)
-    sub.gemm(data, split_k=split_k)
+    sub.gemm(data, split_k=split_k, tile_n=tile_n)
     sub.check_status()
     assert sub.last_kernel().startswith(f"gemm_splitk{split_k}")
     assert_bit_exact(data[6], expected_fp16(oracle, data), what=f"{shape} {sub.last_kernel()}")
