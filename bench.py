@@ -34,7 +34,7 @@ WORKLOADS = {
 }
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
 # captures summarised under profiles/ (one capture per kernel and workload).
-NCU_DRAM_BYTES_PER_LAUNCH = {"c1": 68.3e6, "c2": 268.1e6}
+NCU_DRAM_BYTES_PER_LAUNCH = {"c1": 68.3e6, "c2": 268.1e6, "c3": 130.4e6}
 FP4_DENSE_PEAK_TFLOPS = 9000.0   # nominal dense FP4 tensor peak of one B200 (no measured FP4 figure exists)
 
 
@@ -230,6 +230,12 @@ def main():
         e1.record()
         torch.cuda.synchronize()
         reps.append(e0.elapsed_time(e1))
+    # keep the same load running (untimed) until the clock sampler has seen it for ~0.6 s: the timed
+    # replays alone are a few milliseconds, shorter than nvidia-smi's sampling period
+    t_load = time.perf_counter()
+    while time.perf_counter() - t_load < 0.6:
+        graph.replay()
+        torch.cuda.synchronize()
     S.check_status()
     kernel_name = S.last_kernel()
     reps.sort()

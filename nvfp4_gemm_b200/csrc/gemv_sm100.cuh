@@ -90,7 +90,7 @@ __device__ __forceinline__ void cvt_e4m3x4(uint32_t packed, float (&f)[4]) {
     f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
 }
 
-template <int R>
+template <int R, int UNROLL = (R == 1) ? 4 : (R == 2 ? 2 : 1)>
 __global__ void __launch_bounds__(kGemvThreads) gemv_nvfp4_kernel(const GemvParams p) {
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -114,7 +114,6 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_nvfp4_kernel(const GemvPara
     for (int r = 0; r < R; ++r) sum[r] = 0.f;
 
     const int n_chunks = p.K / 64;
-    constexpr int UNROLL = (R == 1) ? 4 : (R == 2 ? 2 : 1);
     for (int base = 0; base < n_chunks; base += 32 * UNROLL) {
         Chunk32 av[UNROLL][R];
         uint32_t sav[UNROLL][R];

@@ -350,7 +350,12 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* const*
     int cg = cf.cta_group;
     if (cg == 0) cg = (p->m > kBM && p->n % 256 == 0) ? 2 : 1;
     int bn = cf.tile_n;
-    if (bn == 0) bn = (p->n % 256 == 0) ? 256 : 128;
+    if (bn == 0) {
+        bn = (p->n % 256 == 0) ? 256 : 128;
+        // single-CTA tiles that would leave SMs idle: halve the tile width to double the tile count
+        const long long tiles256 = static_cast<long long>((p->m + kBM - 1) / kBM) * (p->n / 256) * p->l;
+        if (cg == 1 && bn == 256 && tiles256 < c->num_sms) bn = 128;
+    }
     if (p->n % bn) return fail(NVFP4_ERR_INVALID_ARGUMENT, "n = %d is not a multiple of tile_n = %d", p->n, bn);
 
     GemmParams g;
@@ -410,7 +415,7 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* const*
             // measured: two CTAs per tile beat four whenever both fit in one wave (the exchange
             // grows with the cluster); four only pays when there are very few tiles
             if (tiles128 * 4 <= c->num_sms / 2 && g.k_tiles >= 16) ks = 4;
-            else if (tiles128 * 2 <= c->num_sms && g.k_tiles >= 4) ks = 2;
+            else if (tiles128 * 2 <= c->num_sms && g.k_tiles >= 16) ks = 2;   // shorter K: one whole tile per CTA wins
         }
     }
     if (ks > 1) {
