@@ -58,7 +58,7 @@ typedef struct nvfp4_problem {
 /* Kernel selection override for tests and tuning; zero in every field = automatic. */
 typedef struct nvfp4_gemm_config {
     int32_t tile_n;    /* 0 auto, 128 or 256 */
-    int32_t epilogue;  /* 0 auto, 1 = 16-byte global stores, 2 = TMA store */
+    int32_t epilogue;  /* 0 auto, 1 = 16-byte global stores, 2 = TMA store, 3 = TMA store with four staging buffers per warp */
     int32_t grid;      /* 0 auto (one CTA per SM), else number of persistent CTAs */
     int32_t cta_group; /* 0 auto, 1 = one CTA per tile, 2 = CTA pair per 256-row tile */
     int32_t split_k;   /* 0 auto, 1 = persistent stream-K kernel, 2 or 4 = cluster split-K (reduce in DSMEM) */
@@ -92,10 +92,11 @@ int nvfp4_matmul(const nvfp4_problem* problem, void* stream);
  * the full row-major output of each GPU (base + rank * n_local), problem->n is the local width and
  * problem->c_row_stride the full width; c_peers[i] are peer-mapped device pointers (stores only;
  * nothing is loaded from another GPU).  The caller synchronises the ranks after the kernel (all
- * ranks' kernels must finish before any rank reads its output).  The reference has no multi-GPU
- * code; no counterpart.
+ * ranks' kernels must finish before any rank reads its output).  cfg may be NULL.  The reference
+ * has no multi-GPU code; no counterpart.
  */
-int nvfp4_gemm_allgather(const nvfp4_problem* problem, void* const* c_peers, int n_peers, void* stream);
+int nvfp4_gemm_allgather(const nvfp4_problem* problem, const nvfp4_gemm_config* cfg, void* const* c_peers, int n_peers,
+                         void* stream);
 
 /*
  * Column-parallel multi-GPU GEMM, last step: an all-gather of per-rank fp16 column blocks leaves

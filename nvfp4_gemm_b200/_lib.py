@@ -69,7 +69,7 @@ def load() -> ctypes.CDLL:
     lib.nvfp4_gemm_static_scratch.restype = c_int
     lib.nvfp4_interleave_column_blocks.argtypes = [c_void_p, c_void_p, c_int64, c_int32, c_int32, c_int64, c_void_p]
     lib.nvfp4_interleave_column_blocks.restype = c_int
-    lib.nvfp4_gemm_allgather.argtypes = [ctypes.POINTER(Problem), ctypes.POINTER(c_void_p), c_int, c_void_p]
+    lib.nvfp4_gemm_allgather.argtypes = [ctypes.POINTER(Problem), ctypes.POINTER(GemmConfig), ctypes.POINTER(c_void_p), c_int, c_void_p]
     lib.nvfp4_gemm_allgather.restype = c_int
     lib.nvfp4_quantize.argtypes = [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int64, c_int64, c_int64, c_void_p]
     lib.nvfp4_quantize.restype = c_int

@@ -85,7 +85,8 @@ struct GemmSmem {
     // Epilogue scratch: TMA-store staging (two 32-row x 128-byte buffers per warp), or the landing
     // area of the cluster split-K exchange.
     static constexpr uint32_t kEpiBytes = EPI_KB * 1024;
-    static constexpr uint32_t kStagingPerWarp = 2 * 32 * 128;
+    static constexpr uint32_t kStagingBufs = TMA_STORE ? (EPI_KB * 1024 / 4) / 4096 : 2;   // 32-row x 128-byte buffers per epilogue warp
+    static constexpr uint32_t kStagingPerWarp = kStagingBufs * 32 * 128;
     // The finisher of a shared tile lands other workers' partials in the (then idle) operand ring.
     static constexpr uint32_t kFixSlots = (STAGES * kStageBytes / kFixChunkBytes) < 12 ? (STAGES * kStageBytes / kFixChunkBytes) : 12;
     static constexpr uint32_t kFixBufs = 12;  // barriers reserved for the landing slots
@@ -525,8 +526,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                     // 32-row staging buffers, overlapping the next tile's MMAs.
 #pragma unroll
                     for (int ci = 0; ci < BN / 64; ++ci) {
-                        // the buffer about to be overwritten was read by the store issued two chunks ago
-                        if (lane == 0) ptx::bulk_wait_group_read<1>();
+                        // the buffer about to be overwritten was read by the store issued kStagingBufs chunks ago
+                        if (lane == 0) ptx::bulk_wait_group_read<S::kStagingBufs - 1>();
                         __syncwarp();
                         uint8_t* buf = staging_gen + store_buf * 4096 + lane * 128;
 #pragma unroll
@@ -541,7 +542,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                                 ptx::tma_store_3d(&p.tma_c_peer[r], staging + store_buf * 4096, nb * BN + ci * 64, mb * kBM + quad * 32, l);
                             ptx::bulk_commit_group();
                         }
-                        store_buf ^= 1u;
+                        store_buf = (store_buf + 1u) % S::kStagingBufs;
                     }
                 } else {
 #pragma unroll 1

@@ -334,7 +334,7 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* const*
     if (cfg) cf = *cfg;
     if (cf.tile_n != 0 && cf.tile_n != 128 && cf.tile_n != 256)
         return fail(NVFP4_ERR_INVALID_ARGUMENT, "tile_n must be 0, 128 or 256");
-    if (cf.epilogue < 0 || cf.epilogue > 2) return fail(NVFP4_ERR_INVALID_ARGUMENT, "epilogue must be 0, 1 or 2");
+    if (cf.epilogue < 0 || cf.epilogue > 3) return fail(NVFP4_ERR_INVALID_ARGUMENT, "epilogue must be 0, 1, 2 or 3");
     if (cf.cta_group < 0 || cf.cta_group > 2) return fail(NVFP4_ERR_INVALID_ARGUMENT, "cta_group must be 0, 1 or 2");
     if (cf.split_k != 0 && cf.split_k != 1 && cf.split_k != 2 && cf.split_k != 4 && cf.split_k != 8)
         return fail(NVFP4_ERR_INVALID_ARGUMENT, "split_k must be 0, 1, 2, 4 or 8");
@@ -395,7 +395,7 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* const*
     if (int rc = get_map(c, make_sf_key(p->sfb_perm, p->n, p->k, p->l, p->sfb_perm_batch_stride, bn / 128), &g.tma_sfb)) return rc;
     g.n_peer = n_peers;
     for (int i = 0; i < n_peers; ++i) g.c_peer[i] = static_cast<__half*>(c_peers[i]);
-    if (epilogue == 2) {
+    if (epilogue >= 2) {
         if (int rc = get_map(c, make_key(p->c, p->n, p->m, p->l, static_cast<uint64_t>(p->c_row_stride) * 2, c_bs, 64, 32,
                                          CU_TENSOR_MAP_DATA_TYPE_FLOAT16),
                              &g.tma_c)) return rc;
@@ -441,14 +441,15 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* const*
 
     const int grid = cf.grid;
     if (cg == 2) {
+        if (bn == 256 && epilogue == 3) return launch_gemm<2, 256, 4, true, 64>(c, 12, g, grid, stream, "gemm_2cta_n256_s4_tmastore4");
         if (bn == 256 && epilogue == 2) return launch_gemm<2, 256, 5, true, 32>(c, 4, g, grid, stream, "gemm_2cta_n256_s5_tmastore");
         if (bn == 256) return launch_gemm<2, 256, 5, false, 32>(c, 5, g, grid, stream, "gemm_2cta_n256_s5_direct");
-        if (epilogue == 2) return launch_gemm<2, 128, 6, true, 32>(c, 6, g, grid, stream, "gemm_2cta_n128_s6_tmastore");
+        if (epilogue >= 2) return launch_gemm<2, 128, 6, true, 32>(c, 6, g, grid, stream, "gemm_2cta_n128_s6_tmastore");
         return launch_gemm<2, 128, 6, false, 32>(c, 7, g, grid, stream, "gemm_2cta_n128_s6_direct");
     }
-    if (bn == 128 && epilogue == 2) return launch_gemm<1, 128, 5, true, 32>(c, 0, g, grid, stream, "gemm_1cta_n128_s5_tmastore");
+    if (bn == 128 && epilogue >= 2) return launch_gemm<1, 128, 5, true, 32>(c, 0, g, grid, stream, "gemm_1cta_n128_s5_tmastore");
     if (bn == 128) return launch_gemm<1, 128, 4, false, 64>(c, 1, g, grid, stream, "gemm_1cta_n128_s4_direct");
-    if (epilogue == 2) return launch_gemm<1, 256, 3, true, 32>(c, 2, g, grid, stream, "gemm_1cta_n256_s3_tmastore");
+    if (epilogue >= 2) return launch_gemm<1, 256, 3, true, 32>(c, 2, g, grid, stream, "gemm_1cta_n256_s3_tmastore");
     return launch_gemm<1, 256, 3, false, 48>(c, 3, g, grid, stream, "gemm_1cta_n256_s3_direct");
 }
 }  // namespace
@@ -459,18 +460,17 @@ int nvfp4_gemm(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* strea
     return gemm_impl(p, cfg, nullptr, 0, stream_v);
 }
 
-int nvfp4_gemm_allgather(const nvfp4_problem* p, void* const* c_peers, int n_peers, void* stream_v) {
+int nvfp4_gemm_allgather(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* const* c_peers, int n_peers, void* stream_v) {
     if (n_peers < 0 || n_peers > 7) return fail(NVFP4_ERR_INVALID_ARGUMENT, "n_peers must be between 0 and 7 (got %d)", n_peers);
     if (n_peers > 0 && !c_peers) return fail(NVFP4_ERR_INVALID_ARGUMENT, "c_peers is NULL");
     for (int i = 0; i < n_peers; ++i)
         if (!c_peers[i] || !aligned(c_peers[i], 16)) return fail(NVFP4_ERR_INVALID_ARGUMENT, "c_peers[%d] must be a 16-byte aligned pointer", i);
-    if (p && p->m <= kBM && n_peers > 0) {
-        // decode shapes would take the cluster split-K kernel; keep them on the persistent kernel,
-        // whose epilogues all know about peers
-        nvfp4_gemm_config cf = {0, 0, 0, 0, 1};
-        return gemm_impl(p, &cf, c_peers, n_peers, stream_v);
-    }
-    return gemm_impl(p, nullptr, c_peers, n_peers, stream_v);
+    // the cluster split-K kernels (decode shapes) finish tiles in their exchange epilogue, which
+    // does know about peers too, but keep this entry on the persistent kernels: one code path
+    nvfp4_gemm_config cf = {0, 0, 0, 0, 0};
+    if (cfg) cf = *cfg;
+    if (cf.split_k == 0) cf.split_k = 1;
+    return gemm_impl(p, &cf, c_peers, n_peers, stream_v);
 }
 
 int nvfp4_gemv(const nvfp4_problem* p, void* stream_v) {

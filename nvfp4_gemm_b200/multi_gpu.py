@@ -154,8 +154,9 @@ class FusedAllGatherGemm:
     (everybody's stores have landed) with the symmetric-memory barrier, which is stream-ordered.
     """
 
-    def __init__(self, m: int, n: int, k: int, group=None, device=None):
+    def __init__(self, m: int, n: int, k: int, group=None, device=None, config=None):
         import ctypes
+        self.config = config
         import os
         # plain peer stores only: do not bind the buffer to an NVLink multicast object
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
@@ -184,7 +185,7 @@ class FusedAllGatherGemm:
         problem = make_problem(tuple(local_data[:6]) + (c_block,))
         stream = torch.cuda.current_stream(self.device).cuda_stream
         self.handle.barrier(channel=0)
-        _lib.check(lib.nvfp4_gemm_allgather(problem, self.peer_array, self.n_peers, stream))
+        _lib.check(lib.nvfp4_gemm_allgather(problem, self.config, self.peer_array, self.n_peers, stream))
         self.handle.barrier(channel=1)
         return self.c_full
 
@@ -209,7 +210,10 @@ def bench_column_parallel(args, w, rank, world, dev, ClockSampler, measured_peak
     fused = None
     if mode == "fused":
         try:
-            fused = FusedAllGatherGemm(m, n, k, device=dev)
+            import os
+            from ._lib import GemmConfig
+            ep = int(os.environ.get("NVFP4_AG_EPILOGUE", "0"))     # experiment knob: 1 vector stores, 2 / 3 TMA stores
+            fused = FusedAllGatherGemm(m, n, k, device=dev, config=GemmConfig(0, ep, 0, 0, 0) if ep else None)
         except Exception as e:  # symmetric memory unavailable on this box: use the NCCL path and say so
             mode = f"nccl (fused path unavailable: {str(e)[:120]})"
     if fused is not None:

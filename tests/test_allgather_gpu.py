@@ -34,7 +34,7 @@ def test_gemm_stores_its_column_block_into_every_peer_buffer(cuda_lib, oracle, m
     begin = rank * n_local
     problem = make_problem(tuple(data[:6]) + (outs[0][:, begin:begin + n_local],))
     peers = (ctypes.c_void_p * n_peers)(*[o.data_ptr() + begin * 2 for o in outs[1:]])
-    _lib.check(cuda_lib.nvfp4_gemm_allgather(problem, peers, n_peers, torch.cuda.current_stream().cuda_stream))
+    _lib.check(cuda_lib.nvfp4_gemm_allgather(problem, None, peers, n_peers, torch.cuda.current_stream().cuda_stream))
     _lib.check(cuda_lib.nvfp4_check_status(torch.cuda.current_stream().cuda_stream))
     a, b, sfa, sfb = oracle.tensors_to_numpy(data)
     exp = oracle.ref_gemm_c(a, b, sfa, sfb)
@@ -50,8 +50,8 @@ def test_allgather_entry_point_rejects_bad_peer_lists(cuda_lib):
     from nvfp4_gemm_b200.submission import make_problem
     data = generate_input(256, 256, 512, 1, 1)
     p = make_problem(data)
-    assert cuda_lib.nvfp4_gemm_allgather(p, None, 2, None) == _lib.NVFP4_ERR_INVALID_ARGUMENT
+    assert cuda_lib.nvfp4_gemm_allgather(p, None, None, 2, None) == _lib.NVFP4_ERR_INVALID_ARGUMENT
     arr = (ctypes.c_void_p * 8)(*[data[6].data_ptr()] * 8)
-    assert cuda_lib.nvfp4_gemm_allgather(p, arr, 8, None) == _lib.NVFP4_ERR_INVALID_ARGUMENT
+    assert cuda_lib.nvfp4_gemm_allgather(p, None, arr, 8, None) == _lib.NVFP4_ERR_INVALID_ARGUMENT
     arr[0] = data[6].data_ptr() + 2
-    assert cuda_lib.nvfp4_gemm_allgather(p, arr, 1, None) == _lib.NVFP4_ERR_INVALID_ARGUMENT
+    assert cuda_lib.nvfp4_gemm_allgather(p, None, arr, 1, None) == _lib.NVFP4_ERR_INVALID_ARGUMENT

@@ -39,7 +39,7 @@ def test_custom_kernel_matches_oracle_bit_exact(sub, oracle, shape):
 
 VARIANTS = [  # (cta_group, tile_n, epilogue, split_k)
     (1, 128, 1, 1), (1, 128, 2, 1), (1, 256, 1, 1), (1, 256, 2, 1),     # one CTA per tile, stream-K
-    (2, 128, 1, 1), (2, 128, 2, 1), (2, 256, 1, 1), (2, 256, 2, 1),     # CTA pair per 256-row tile
+    (2, 128, 1, 1), (2, 128, 2, 1), (2, 256, 1, 1), (2, 256, 2, 1), (2, 256, 3, 1),   # CTA pair per 256-row tile
 ]
 
 
