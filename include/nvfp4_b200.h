@@ -99,6 +99,14 @@ int nvfp4_gemm_allgather(const nvfp4_problem* problem, const nvfp4_gemm_config* 
                          void* stream);
 
 /*
+ * Strided device-to-device copy (one cudaMemcpy2DAsync: `rows` pieces of `width_bytes`), used to
+ * push a rank's column block of C into a peer GPU's row-major output with the copy engines while
+ * the SMs compute the next row panel.  dst may be peer-mapped memory.  No counterpart in the
+ * reference (single GPU).
+ */
+int nvfp4_copy_2d(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch, int64_t width_bytes, int64_t rows, void* stream);
+
+/*
  * Column-parallel multi-GPU GEMM, last step: an all-gather of per-rank fp16 column blocks leaves
  * [blocks][rows][n_local] in memory; this writes the row-major [rows][blocks * n_local] matrix
  * (row stride dst_row_stride elements).  The reference has no multi-GPU code; no counterpart.

@@ -561,6 +561,15 @@ int nvfp4_permute_scales(const void* plain, void* permuted, int32_t rows, int32_
     return NVFP4_OK;
 }
 
+int nvfp4_copy_2d(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch, int64_t width_bytes, int64_t rows, void* stream_v) {
+    if (!dst || !src) return fail(NVFP4_ERR_INVALID_ARGUMENT, "dst and src must not be NULL");
+    if (width_bytes < 1 || rows < 1 || dst_pitch < width_bytes || src_pitch < width_bytes)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "width_bytes, rows >= 1 and both pitches >= width_bytes required");
+    CUDA_TRY(cudaMemcpy2DAsync(dst, static_cast<size_t>(dst_pitch), src, static_cast<size_t>(src_pitch), static_cast<size_t>(width_bytes),
+                               static_cast<size_t>(rows), cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream_v)));
+    return NVFP4_OK;
+}
+
 int nvfp4_quantize(const void* x, int32_t x_is_bf16, void* packed, void* sf_plain, void* sf_permuted, int32_t rows, int32_t k,
                    int64_t x_row_stride, int64_t packed_row_stride, int64_t sf_plain_row_stride, void* stream_v) {
     if (!x || !packed) return fail(NVFP4_ERR_INVALID_ARGUMENT, "x and packed must not be NULL");

@@ -190,6 +190,58 @@ class FusedAllGatherGemm:
         return self.c_full
 
 
+class CopyEngineAllGatherGemm:
+    """Column-parallel GEMM whose column blocks travel by copy engine.  The rank's GEMM runs row
+    panel by row panel straight into its own columns of the full row-major C (symmetric memory);
+    as soon as a panel is done, one strided device-to-device copy per peer (cudaMemcpy2DAsync on a
+    stream of its own) pushes that panel's column block into the same place of the peer's C while
+    the SMs compute the next panel.  No staging, no re-layout, no SM spent on the transfer.
+    """
+
+    def __init__(self, m: int, n: int, k: int, group=None, device=None, panels: int = 4):
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.shard = plan_shard(n, self.world, self.rank)
+        self.m, self.n, self.k = m, n, k
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.c_sym = symm_mem.empty((m * n,), dtype=torch.float16, device=self.device)
+        self.handle = symm_mem.rendezvous(self.c_sym, self.group)
+        self.c_full = self.c_sym.view(1, m, n).permute(1, 2, 0)
+        self.panels = row_panels(m, panels)
+        self.peer_bases = [int(self.handle.buffer_ptrs[r]) for r in range(self.world) if r != self.rank]
+        self.copy_streams = [torch.cuda.Stream(device=self.device) for _ in self.peer_bases]
+
+    def __call__(self, local_data) -> torch.Tensor:
+        from . import _lib
+        from .submission import custom_kernel
+        lib = _lib.load()
+        a, b, sfa, sfb, sfa_perm, sfb_perm, _ = local_data
+        n, nl = self.n, self.shard.n_local
+        compute = torch.cuda.current_stream(self.device)
+        self.handle.barrier(channel=0)                     # nobody still reads the previous result
+        local_base = self.c_sym.data_ptr()
+        for (p0, p1) in self.panels:
+            rb0, rb1 = p0 // 128, (p1 + 127) // 128
+            c_panel = self.c_full[p0:p1, self.shard.begin:self.shard.end]
+            custom_kernel((a[p0:p1], b, sfa[p0:p1], sfb, sfa_perm[:, :, rb0:rb1], sfb_perm, c_panel))
+            done = torch.cuda.Event()
+            done.record(compute)
+            off = (p0 * n + self.shard.begin) * 2
+            for base, stream in zip(self.peer_bases, self.copy_streams):
+                stream.wait_event(done)
+                _lib.check(lib.nvfp4_copy_2d(base + off, n * 2, local_base + off, n * 2, nl * 2, p1 - p0, stream.cuda_stream))
+        for stream in self.copy_streams:
+            ev = torch.cuda.Event()
+            ev.record(stream)
+            compute.wait_event(ev)
+        self.handle.barrier(channel=1)                     # every rank's pushes have landed
+        return self.c_full
+
+
 def bench_column_parallel(args, w, rank, world, dev, ClockSampler, measured_peaks, algorithmic_flops):
     """`bench.py --gpus N` for N > 1: strong scaling of the one partitioned workload."""
     import json
@@ -216,6 +268,8 @@ def bench_column_parallel(args, w, rank, world, dev, ClockSampler, measured_peak
             fused = FusedAllGatherGemm(m, n, k, device=dev, config=GemmConfig(0, ep, 0, 0, 0) if ep else None)
         except Exception as e:  # symmetric memory unavailable on this box: use the NCCL path and say so
             mode = f"nccl (fused path unavailable: {str(e)[:120]})"
+    if mode == "ce":
+        fused = CopyEngineAllGatherGemm(m, n, k, device=dev, panels=int(__import__("os").environ.get("NVFP4_AG_PANELS", "4")))
     if fused is not None:
         c_full = [fused.c_full]
 
@@ -290,7 +344,9 @@ def bench_column_parallel(args, w, rank, world, dev, ClockSampler, measured_peak
         line = dict(metric="nvfp4_matmul_throughput", value=tflops, unit="TFLOP/s", n_gpus=world, steps=args.steps,
                     warmup=args.warmup, ms_per_step=ms_per_step, higher_is_better=True, scaling="strong", vs_baseline=None,
                     dtype="e2m1 x ue4m3 -> f32 -> f16", data="synthetic",
-                    config=dict(workload=w["name"], parallelism=(f"column-parallel over N on {world} GPUs; all-gather fused into the GEMM epilogue (peer stores over NVLink)"
+                    config=dict(workload=w["name"], parallelism=(f"column-parallel over N on {world} GPUs; column blocks pushed to the peers by copy engine per row panel, overlapping the next panel's GEMM"
+                                             if mode == "ce" else
+                                             f"column-parallel over N on {world} GPUs; all-gather fused into the GEMM epilogue (peer stores over NVLink)"
                                              if fused is not None else
                                              f"column-parallel over N on {world} GPUs, NCCL all-gather of fp16 blocks, 4 row panels, {mode}"),
                                 timing="CUDA events, max over ranks; 2 rotating input sets (302 MB per rank set) > L2",
