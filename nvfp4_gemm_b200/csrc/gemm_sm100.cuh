@@ -54,8 +54,8 @@ struct GemmParams {
     CUtensorMap tma_sfb; // permuted scales of B, same view, box {128, 4, BN/128, 1}
     __half* c;
     // Fused all-gather (column-parallel multi-GPU): every finished piece of C is also stored into
-    // the same position of n_peer other GPUs' output buffers (peer-mapped memory, stores only).
-    CUtensorMap tma_c_peer[7];
+    // the same position of n_peer other GPUs' output buffers (peer-mapped memory, plain vector
+    // stores only; nothing is ever loaded from a peer).
     __half* c_peer[7];
     int n_peer;
     float* scratch;      // partial-tile slots [worker][head|tail][cta of pair][BN/4][128][4] fp32
@@ -538,9 +538,30 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                         __syncwarp();
                         if (lane == 0 && mb * kBM + quad * 32 < p.M) {  // rows past M inside the box are clipped; one fixed lane owns the bulk groups
                             ptx::tma_store_3d(&p.tma_c, staging + store_buf * 4096, nb * BN + ci * 64, mb * kBM + quad * 32, l);
-                            for (int r = 0; r < p.n_peer; ++r)
-                                ptx::tma_store_3d(&p.tma_c_peer[r], staging + store_buf * 4096, nb * BN + ci * 64, mb * kBM + quad * 32, l);
                             ptx::bulk_commit_group();
+                        }
+                        if (p.n_peer > 0) {
+                            // Peers get the same 32 x 128-byte block with plain vector stores read back
+                            // from the staging buffer: a warp instruction covers four full 128-byte
+                            // rows.  (One TMA store per peer was tried first: with a tensor map per
+                            // destination the stores crawled once there were more than a few maps.)
+                            const int sub = lane >> 3, piece = lane & 7;
+                            uint4 q[8];
+#pragma unroll
+                            for (int it = 0; it < 8; ++it) {
+                                const int rr = it * 4 + sub;
+                                q[it] = *reinterpret_cast<const uint4*>(staging_gen + store_buf * 4096 + rr * 128 + ((piece ^ (rr & 7)) << 4));
+                            }
+                            const int row_base = mb * kBM + quad * 32;
+                            for (int pi = 0; pi < p.n_peer; ++pi) {
+                                const int r = (pi + static_cast<int>(blockIdx.x)) % p.n_peer;   // spread the start over CTAs
+                                __half* dst = p.c_peer[r] + l * p.c_batch_stride + nb * BN + ci * 64 + piece * 8;
+#pragma unroll
+                                for (int it = 0; it < 8; ++it) {
+                                    const int grow = row_base + it * 4 + sub;
+                                    if (grow < p.M) *reinterpret_cast<uint4*>(dst + static_cast<long long>(grow) * p.c_row_stride) = q[it];
+                                }
+                            }
                         }
                         store_buf = (store_buf + 1u) % S::kStagingBufs;
                     }

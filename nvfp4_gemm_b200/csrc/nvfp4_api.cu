@@ -399,10 +399,6 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* const*
         if (int rc = get_map(c, make_key(p->c, p->n, p->m, p->l, static_cast<uint64_t>(p->c_row_stride) * 2, c_bs, 64, 32,
                                          CU_TENSOR_MAP_DATA_TYPE_FLOAT16),
                              &g.tma_c)) return rc;
-        for (int i = 0; i < n_peers; ++i)
-            if (int rc = get_map(c, make_key(c_peers[i], p->n, p->m, p->l, static_cast<uint64_t>(p->c_row_stride) * 2, c_bs, 64, 32,
-                                             CU_TENSOR_MAP_DATA_TYPE_FLOAT16),
-                                 &g.tma_c_peer[i])) return rc;
     }
 
     // Decode shapes (one 128-row block, fewer tiles than half the SMs): split K across a cluster

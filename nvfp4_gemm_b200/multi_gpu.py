@@ -262,14 +262,11 @@ def bench_column_parallel(args, w, rank, world, dev, ClockSampler, measured_peak
     fused = None
     if mode == "fused":
         try:
-            import os
-            from ._lib import GemmConfig
-            ep = int(os.environ.get("NVFP4_AG_EPILOGUE", "0"))     # experiment knob: 1 vector stores, 2 / 3 TMA stores
-            fused = FusedAllGatherGemm(m, n, k, device=dev, config=GemmConfig(0, ep, 0, 0, 0) if ep else None)
+            fused = FusedAllGatherGemm(m, n, k, device=dev)
         except Exception as e:  # symmetric memory unavailable on this box: use the NCCL path and say so
             mode = f"nccl (fused path unavailable: {str(e)[:120]})"
     if mode == "ce":
-        fused = CopyEngineAllGatherGemm(m, n, k, device=dev, panels=int(__import__("os").environ.get("NVFP4_AG_PANELS", "4")))
+        fused = CopyEngineAllGatherGemm(m, n, k, device=dev, panels=4)
     if fused is not None:
         c_full = [fused.c_full]
 
