@@ -160,7 +160,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
-    ap.add_argument("--allgather", default="fused", choices=["fused", "ce", "nccl"],
+    ap.add_argument("--allgather", default="fused", choices=["fused", "push", "pull", "ce", "nccl"],
                     help="N > 1: all-gather fused into the GEMM epilogue (peer stores) or NCCL + re-layout")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary per-config table")

@@ -99,6 +99,19 @@ int nvfp4_gemm_allgather(const nvfp4_problem* problem, const nvfp4_gemm_config* 
                          void* stream);
 
 /*
+ * All-gather by a copy kernel: copies rows [row0, row0 + rows) of n_blocks (<= 7) column blocks,
+ * each n_local fp16 wide inside a row-major matrix of row_stride elements, from src_blocks[i] to
+ * dst_blocks[i].  Either side may be another GPU's peer-mapped output (already offset to the
+ * block): "pull" reads the blocks other GPUs computed into the same place of the local output,
+ * "push" writes this GPU's block (every src_blocks[i] the same local pointer) into the peers'
+ * outputs.  Plain coalesced 16-byte loads (eight in flight per thread) and stores; ctas = 0 picks
+ * two CTAs per SM.  The caller orders it after the producers' kernels (event or cross-rank
+ * barrier).  No counterpart in the reference (single GPU).
+ */
+int nvfp4_copy_column_blocks(void* const* dst_blocks, const void* const* src_blocks, int32_t n_blocks, int64_t row0, int64_t rows,
+                             int32_t n_local, int64_t row_stride, int32_t ctas, void* stream);
+
+/*
  * Strided device-to-device copy (one cudaMemcpy2DAsync: `rows` pieces of `width_bytes`), used to
  * push a rank's column block of C into a peer GPU's row-major output with the copy engines while
  * the SMs compute the next row panel.  dst may be peer-mapped memory.  No counterpart in the

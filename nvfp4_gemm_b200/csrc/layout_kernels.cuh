@@ -28,6 +28,51 @@ __global__ void __launch_bounds__(256) interleave_column_blocks_kernel(const uin
     }
 }
 
+// All-gather by a copy kernel: rows [row0, row0 + rows) of up to seven column blocks go from
+// src[i] to dst[i] (same offsets inside row-major matrices of one row stride).  Either side may be
+// peer-mapped memory of another GPU.  16 bytes per thread and access, a warp reads and writes 512
+// contiguous bytes of one row.
+__device__ __forceinline__ uint4 ld_nc_na_v4(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+struct BlockCopyParams {
+    const uint4* src[7];   // source matrix base + the block's column offset
+    uint4* dst[7];         // destination matrix base + the same offset
+    int n_src;
+};
+__global__ void __launch_bounds__(256) copy_column_blocks_kernel(const BlockCopyParams pp, long long row0, unsigned rows, unsigned vec_per_row,
+                                                                 long long row_stride_vec) {
+    // Loads over NVLink have a round trip of microseconds: every thread keeps kInFlight of them
+    // outstanding before its first store.
+    constexpr int kInFlight = 8;
+    const unsigned per_src = rows * vec_per_row;
+    const unsigned total = per_src * static_cast<unsigned>(pp.n_src);
+    const unsigned chunk = blockDim.x * kInFlight;
+    for (unsigned base = blockIdx.x * chunk; base < total; base += gridDim.x * chunk) {
+        uint4 v[kInFlight];
+        long long off[kInFlight];
+        int src[kInFlight];
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u) {
+            const unsigned i = base + u * blockDim.x + threadIdx.x;
+            src[u] = -1;
+            if (i < total) {
+                const unsigned s = i / per_src;
+                const unsigned rem = i - s * per_src;
+                const unsigned row = rem / vec_per_row;
+                src[u] = static_cast<int>(s);
+                off[u] = (row0 + row) * row_stride_vec + (rem - row * vec_per_row);
+                v[u] = ld_nc_na_v4(pp.src[s] + off[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u)
+            if (src[u] >= 0) pp.dst[src[u]][off[u]] = v[u];
+    }
+}
+
 // One thread produces 16 bytes of an atom: the four scales of rows {r32 + 32*j, j = 0..3}... laid
 // out as [r32][j][k4]; it reads four 4-byte words (one per 32-row group) from the plain layout.
 __global__ void __launch_bounds__(256) permute_scales_kernel(const uint8_t* __restrict__ plain, uint8_t* __restrict__ perm,

@@ -557,6 +557,31 @@ int nvfp4_permute_scales(const void* plain, void* permuted, int32_t rows, int32_
     return NVFP4_OK;
 }
 
+int nvfp4_copy_column_blocks(void* const* dst_blocks, const void* const* src_blocks, int32_t n_blocks, int64_t row0, int64_t rows,
+                             int32_t n_local, int64_t row_stride, int32_t ctas, void* stream_v) {
+    if (n_blocks < 1 || n_blocks > 7 || !dst_blocks || !src_blocks) return fail(NVFP4_ERR_INVALID_ARGUMENT, "1..7 blocks required");
+    if (rows < 1 || row0 < 0 || n_local < 8 || n_local % 8 || row_stride % 8 || row_stride < n_local)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "rows >= 1, n_local and row_stride multiples of 8 elements, row_stride >= n_local required");
+    BlockCopyParams pp;
+    pp.n_src = n_blocks;
+    for (int i = 0; i < n_blocks; ++i) {
+        if (!dst_blocks[i] || !src_blocks[i] || !aligned(dst_blocks[i], 16) || !aligned(src_blocks[i], 16))
+            return fail(NVFP4_ERR_INVALID_ARGUMENT, "block %d: pointers must be non-NULL and 16-byte aligned", i);
+        pp.src[i] = static_cast<const uint4*>(src_blocks[i]);
+        pp.dst[i] = static_cast<uint4*>(dst_blocks[i]);
+    }
+    int dev = 0, sms = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (rows * (n_local / 8) * n_blocks >= (1ll << 31)) return fail(NVFP4_ERR_INVALID_ARGUMENT, "more than 2^31 16-byte units in one call");
+    int grid = ctas > 0 ? ctas : sms * 2;
+    copy_column_blocks_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream_v)>>>(pp, row0, static_cast<unsigned>(rows),
+                                                                                     static_cast<unsigned>(n_local / 8), row_stride / 8);
+    CUDA_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    return NVFP4_OK;
+}
+
 int nvfp4_copy_2d(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch, int64_t width_bytes, int64_t rows, void* stream_v) {
     if (!dst || !src) return fail(NVFP4_ERR_INVALID_ARGUMENT, "dst and src must not be NULL");
     if (width_bytes < 1 || rows < 1 || dst_pitch < width_bytes || src_pitch < width_bytes)

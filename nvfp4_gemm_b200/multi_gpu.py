@@ -242,6 +242,81 @@ class CopyEngineAllGatherGemm:
         return self.c_full
 
 
+class PanelAllGatherGemm:
+    """Column-parallel GEMM with the exchange done by this library's copy kernel, row panel by row
+    panel, on a second stream while the tensor cores work on the next panel.  Every rank runs its
+    GEMM straight into its own columns of the full row-major C (symmetric memory); nothing is
+    staged or re-laid-out.
+
+    direction="push": after a panel's GEMM (stream order, no cross-rank wait) the copy kernel
+    writes the panel of this rank's column block into every peer's C (stores over NVLink).
+    direction="pull": after a panel, a stream-ordered cross-rank barrier tells everyone that this
+    panel exists on every rank, and the copy kernel reads the other ranks' blocks of the panel from
+    their peer-mapped C (loads over NVLink).
+    """
+
+    def __init__(self, m: int, n: int, k: int, group=None, device=None, panels: int = 4, copy_ctas: int = 0, direction: str = "push"):
+        import ctypes
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+        if direction not in ("push", "pull"):
+            raise ValueError("direction must be 'push' or 'pull'")
+        self.direction = direction
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if self.world > 8:
+            raise ValueError("at most 8 GPUs (7 peers)")
+        self.shard = plan_shard(n, self.world, self.rank)
+        self.m, self.n, self.k = m, n, k
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.c_sym = symm_mem.empty((m * n,), dtype=torch.float16, device=self.device)
+        self.handle = symm_mem.rendezvous(self.c_sym, self.group)
+        self.c_full = self.c_sym.view(1, m, n).permute(1, 2, 0)
+        self.panels = row_panels(m, panels)
+        self.copy_ctas = copy_ctas
+        self.copy_stream = torch.cuda.Stream(device=self.device)
+        nl = self.shard.n_local
+        # peer order starts with the next rank, so that at any moment the ranks talk to different peers
+        peers = [(self.rank + 1 + i) % self.world for i in range(self.world - 1)]
+        local = self.c_sym.data_ptr()
+        if direction == "pull":
+            src = [int(self.handle.buffer_ptrs[r]) + r * nl * 2 for r in peers]
+            dst = [local + r * nl * 2 for r in peers]
+        else:
+            src = [local + self.rank * nl * 2 for _ in peers]
+            dst = [int(self.handle.buffer_ptrs[r]) + self.rank * nl * 2 for r in peers]
+        self.src = (ctypes.c_void_p * len(peers))(*src)
+        self.dst = (ctypes.c_void_p * len(peers))(*dst)
+        self.n_blocks = len(peers)
+
+    def __call__(self, local_data) -> torch.Tensor:
+        from . import _lib
+        from .submission import custom_kernel
+        lib = _lib.load()
+        a, b, sfa, sfb, sfa_perm, sfb_perm, _ = local_data
+        compute = torch.cuda.current_stream(self.device)
+        self.handle.barrier(channel=0)                     # nobody still reads the previous result
+        for idx, (p0, p1) in enumerate(self.panels):
+            rb0, rb1 = p0 // 128, (p1 + 127) // 128
+            c_panel = self.c_full[p0:p1, self.shard.begin:self.shard.end]
+            custom_kernel((a[p0:p1], b, sfa[p0:p1], sfb, sfa_perm[:, :, rb0:rb1], sfb_perm, c_panel))
+            if self.direction == "pull":
+                self.handle.barrier(channel=1 + idx % 2)   # this panel now exists on every rank
+            ready = torch.cuda.Event()
+            ready.record(compute)
+            self.copy_stream.wait_event(ready)
+            _lib.check(lib.nvfp4_copy_column_blocks(self.dst, self.src, self.n_blocks, p0, p1 - p0, self.shard.n_local, self.n,
+                                                    self.copy_ctas, self.copy_stream.cuda_stream))
+        done = torch.cuda.Event()
+        done.record(self.copy_stream)
+        compute.wait_event(done)
+        if self.direction == "push":
+            self.handle.barrier(channel=1)                 # every rank's blocks have landed here
+        return self.c_full
+
+
 def bench_column_parallel(args, w, rank, world, dev, ClockSampler, measured_peaks, algorithmic_flops):
     """`bench.py --gpus N` for N > 1: strong scaling of the one partitioned workload."""
     import json
@@ -267,6 +342,8 @@ def bench_column_parallel(args, w, rank, world, dev, ClockSampler, measured_peak
             mode = f"nccl (fused path unavailable: {str(e)[:120]})"
     if mode == "ce":
         fused = CopyEngineAllGatherGemm(m, n, k, device=dev, panels=4)
+    if mode in ("pull", "push"):
+        fused = PanelAllGatherGemm(m, n, k, device=dev, panels=4, direction=mode)
     if fused is not None:
         c_full = [fused.c_full]
 
@@ -343,6 +420,10 @@ def bench_column_parallel(args, w, rank, world, dev, ClockSampler, measured_peak
                     dtype="e2m1 x ue4m3 -> f32 -> f16", data="synthetic",
                     config=dict(workload=w["name"], parallelism=(f"column-parallel over N on {world} GPUs; column blocks pushed to the peers by copy engine per row panel, overlapping the next panel's GEMM"
                                              if mode == "ce" else
+                                             f"column-parallel over N on {world} GPUs; each rank pulls the other ranks' column blocks per row panel with its own copy kernel (loads over NVLink), overlapping the next panel's GEMM"
+                                             if mode == "pull" else
+                                             f"column-parallel over N on {world} GPUs; each rank pushes its column block to the peers per row panel with its own copy kernel (stores over NVLink), overlapping the next panel's GEMM"
+                                             if mode == "push" else
                                              f"column-parallel over N on {world} GPUs; all-gather fused into the GEMM epilogue (peer stores over NVLink)"
                                              if fused is not None else
                                              f"column-parallel over N on {world} GPUs, NCCL all-gather of fp16 blocks, 4 row panels, {mode}"),
