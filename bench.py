@@ -160,8 +160,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
-    ap.add_argument("--allgather", default="fused", choices=["fused", "push", "pull", "ce", "nccl"],
-                    help="N > 1: all-gather fused into the GEMM epilogue (peer stores) or NCCL + re-layout")
+    ap.add_argument("--allgather", default="auto", choices=["auto", "fused", "push", "pull", "ce", "nccl"],
+                    help="N > 1: how the column blocks are exchanged.  fused = peer stores in the GEMM epilogue; push / pull = "
+                         "this library's copy kernel per row panel on a second stream; ce = copy engines; nccl = NCCL + re-layout; "
+                         "auto = fused on 2 GPUs, push on more (the measured best of each)")
+    ap.add_argument("--panels", type=int, default=4, help="N > 1: row panels the exchange is pipelined over (all modes but fused)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary per-config table")
     args = ap.parse_args()

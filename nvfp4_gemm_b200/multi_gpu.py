@@ -242,6 +242,22 @@ class CopyEngineAllGatherGemm:
         return self.c_full
 
 
+def plan_block_copies(rank: int, world: int, n_local: int, local_ptr: int, buffer_ptrs, direction: str):
+    """Source and destination addresses of the copy kernel's column blocks (fp16, so a block starts
+    2 * n_local * owner bytes into a row).  The peer order starts with the next rank, so that at any
+    moment the ranks talk to different peers.  Returns (peers, src, dst)."""
+    peers = [(rank + 1 + i) % world for i in range(world - 1)]
+    if direction == "pull":      # the blocks the peers own, from their C into mine
+        src = [buffer_ptrs[r] + r * n_local * 2 for r in peers]
+        dst = [local_ptr + r * n_local * 2 for r in peers]
+    elif direction == "push":    # the block I own, from my C into theirs
+        src = [local_ptr + rank * n_local * 2 for _ in peers]
+        dst = [buffer_ptrs[r] + rank * n_local * 2 for r in peers]
+    else:
+        raise ValueError("direction must be 'push' or 'pull'")
+    return peers, src, dst
+
+
 class PanelAllGatherGemm:
     """Column-parallel GEMM with the exchange done by this library's copy kernel, row panel by row
     panel, on a second stream while the tensor cores work on the next panel.  Every rank runs its
@@ -277,16 +293,8 @@ class PanelAllGatherGemm:
         self.panels = row_panels(m, panels)
         self.copy_ctas = copy_ctas
         self.copy_stream = torch.cuda.Stream(device=self.device)
-        nl = self.shard.n_local
-        # peer order starts with the next rank, so that at any moment the ranks talk to different peers
-        peers = [(self.rank + 1 + i) % self.world for i in range(self.world - 1)]
-        local = self.c_sym.data_ptr()
-        if direction == "pull":
-            src = [int(self.handle.buffer_ptrs[r]) + r * nl * 2 for r in peers]
-            dst = [local + r * nl * 2 for r in peers]
-        else:
-            src = [local + self.rank * nl * 2 for _ in peers]
-            dst = [int(self.handle.buffer_ptrs[r]) + self.rank * nl * 2 for r in peers]
+        peers, src, dst = plan_block_copies(self.rank, self.world, self.shard.n_local, self.c_sym.data_ptr(),
+                                            [int(p) for p in self.handle.buffer_ptrs], direction)
         self.src = (ctypes.c_void_p * len(peers))(*src)
         self.dst = (ctypes.c_void_p * len(peers))(*dst)
         self.n_blocks = len(peers)
@@ -317,6 +325,13 @@ class PanelAllGatherGemm:
         return self.c_full
 
 
+def best_allgather_mode(world: int) -> str:
+    """Measured on B200 / NVSwitch for the 8192 x 28672 x 8192 job: with two GPUs the GEMM dominates
+    and the epilogue's peer stores hide best; from four GPUs on the exchange dominates and the copy
+    kernel pushing finished row panels keeps the links fuller than the epilogue does."""
+    return "fused" if world <= 2 else "push"
+
+
 def bench_column_parallel(args, w, rank, world, dev, ClockSampler, measured_peaks, algorithmic_flops):
     """`bench.py --gpus N` for N > 1: strong scaling of the one partitioned workload."""
     import json
@@ -333,17 +348,20 @@ def bench_column_parallel(args, w, rank, world, dev, ClockSampler, measured_peak
         local = shard_inputs(full, shard)
         sets.append(tuple(to_device_same_layout(t, dev) if j < 6 else None for j, t in enumerate(local)))
         del full
-    mode = getattr(args, "allgather", "fused")
+    mode = getattr(args, "allgather", "auto")
+    if mode == "auto":
+        mode = best_allgather_mode(world)
     fused = None
-    if mode == "fused":
-        try:
+    panels = max(1, int(getattr(args, "panels", 4)))
+    try:
+        if mode == "fused":
             fused = FusedAllGatherGemm(m, n, k, device=dev)
-        except Exception as e:  # symmetric memory unavailable on this box: use the NCCL path and say so
-            mode = f"nccl (fused path unavailable: {str(e)[:120]})"
-    if mode == "ce":
-        fused = CopyEngineAllGatherGemm(m, n, k, device=dev, panels=4)
-    if mode in ("pull", "push"):
-        fused = PanelAllGatherGemm(m, n, k, device=dev, panels=4, direction=mode)
+        elif mode == "ce":
+            fused = CopyEngineAllGatherGemm(m, n, k, device=dev, panels=panels)
+        elif mode in ("pull", "push"):
+            fused = PanelAllGatherGemm(m, n, k, device=dev, panels=panels, direction=mode)
+    except Exception as e:  # symmetric memory unavailable on this box: use the NCCL path and say so
+        mode = f"nccl ({mode} path unavailable: {str(e)[:120]})"
     if fused is not None:
         c_full = [fused.c_full]
 
@@ -351,7 +369,7 @@ def bench_column_parallel(args, w, rank, world, dev, ClockSampler, measured_peak
             fused(sets[i % n_sets])
     else:
         c_full = [torch.empty((1, m, n), dtype=torch.float16, device=dev).permute(1, 2, 0)]
-        plan = ColumnParallelGemm(m, n, k, device=dev, panels=4)
+        plan = ColumnParallelGemm(m, n, k, device=dev, panels=panels)
 
         def step(i):
             plan(sets[i % n_sets], c_full[0])
@@ -422,11 +440,11 @@ def bench_column_parallel(args, w, rank, world, dev, ClockSampler, measured_peak
                                              if mode == "ce" else
                                              f"column-parallel over N on {world} GPUs; each rank pulls the other ranks' column blocks per row panel with its own copy kernel (loads over NVLink), overlapping the next panel's GEMM"
                                              if mode == "pull" else
-                                             f"column-parallel over N on {world} GPUs; each rank pushes its column block to the peers per row panel with its own copy kernel (stores over NVLink), overlapping the next panel's GEMM"
+                                             f"column-parallel over N on {world} GPUs; each rank pushes its column block to the peers per row panel ({panels} panels) with its own copy kernel (stores over NVLink), overlapping the next panel's GEMM"
                                              if mode == "push" else
                                              f"column-parallel over N on {world} GPUs; all-gather fused into the GEMM epilogue (peer stores over NVLink)"
                                              if fused is not None else
-                                             f"column-parallel over N on {world} GPUs, NCCL all-gather of fp16 blocks, 4 row panels, {mode}"),
+                                             f"column-parallel over N on {world} GPUs, NCCL all-gather of fp16 blocks, {panels} row panels, {mode}"),
                                 timing="CUDA events, max over ranks; 2 rotating input sets (302 MB per rank set) > L2",
                                 gemm_only_ms_per_rank=float(gemm_ms.item()),
                                 gemm_only_tflops_per_gpu=flops / world / (float(gemm_ms.item()) * 1e-3) / 1e12,

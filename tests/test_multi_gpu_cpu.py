@@ -75,3 +75,29 @@ def test_shard_plan_and_panels():
     assert row_panels(100, 4) == [(0, 100)]
     cover = row_panels(4097, 3)
     assert cover[0][0] == 0 and cover[-1][1] == 4097 and all(a[1] == b[0] for a, b in zip(cover, cover[1:]))
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_block_copy_plan_covers_every_foreign_block_once(world):
+    """The copy kernel's address lists: pull reads each peer's own block into the same place of the
+    local output, push writes the local block into the same place of each peer's output; at a given
+    position of the list every rank addresses a different peer."""
+    from nvfp4_gemm_b200.multi_gpu import best_allgather_mode, plan_block_copies
+    n_local = 256
+    bases = [0x10000000 * (r + 1) for r in range(world)]
+    order = []
+    for rank in range(world):
+        peers, src, dst = plan_block_copies(rank, world, n_local, bases[rank], bases, "pull")
+        assert sorted(peers) == [r for r in range(world) if r != rank]
+        for r, s, d in zip(peers, src, dst):
+            assert s == bases[r] + r * n_local * 2 and d == bases[rank] + r * n_local * 2
+        peers2, src2, dst2 = plan_block_copies(rank, world, n_local, bases[rank], bases, "push")
+        assert peers2 == peers
+        for r, s, d in zip(peers2, src2, dst2):
+            assert s == bases[rank] + rank * n_local * 2 and d == bases[r] + rank * n_local * 2
+        order.append(peers)
+    for pos in range(world - 1):
+        assert sorted(o[pos] for o in order) == list(range(world))
+    with pytest.raises(ValueError):
+        plan_block_copies(0, world, n_local, bases[0], bases, "sideways")
+    assert best_allgather_mode(2) == "fused" and best_allgather_mode(8) == "push"
