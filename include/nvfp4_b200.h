@@ -137,6 +137,24 @@ int nvfp4_permute_scales(const void* plain, void* permuted, int32_t rows, int32_
                          int64_t plain_batch_stride, int64_t permuted_batch_stride, void* stream);
 
 /*
+ * The way back: permuted atoms -> plain [l][rows][k/16] (same argument meaning and checks as
+ * nvfp4_permute_scales; padding rows of the atoms are dropped).  No counterpart in the reference.
+ */
+int nvfp4_unpermute_scales(const void* permuted, void* plain, int32_t rows, int32_t k, int32_t l, int64_t plain_row_stride,
+                           int64_t plain_batch_stride, int64_t permuted_batch_stride, void* stream);
+
+/*
+ * Validator for the two scale tensors one operator call carries (template.py:11-14 passes both
+ * and the reference's kernels trust whichever they read): compares plain with permuted on the
+ * device.  result points to two 64-bit words in DEVICE memory, written in stream order:
+ * result[0] = number of scale bytes that differ, result[1] = the smallest linear index
+ * ((batch * rows + row) * (k/16) + scale column) of one, or 2^64-1 when none.  Nothing
+ * synchronises; read result after the stream has.
+ */
+int nvfp4_compare_scale_layouts(const void* plain, const void* permuted, int32_t rows, int32_t k, int32_t l, int64_t plain_row_stride,
+                                int64_t plain_batch_stride, int64_t permuted_batch_stride, uint64_t* result, void* stream);
+
+/*
  * NVFP4 quantiser, the step that produces the operator's inputs: fp16 (x_is_bf16 = 0) or bf16
  * [rows][k] -> packed e2m1 [rows][k/2] plus one e4m3 scale per 16 elements, written in the plain
  * layout (sf_plain, may be NULL) and / or the permuted atom layout (sf_permuted, may be NULL;

@@ -21,6 +21,7 @@ EXPORTED_SYMBOLS = (
     "nvfp4_selftest_bounded_wait", "nvfp4_scratch_bytes", "nvfp4_launch_count", "nvfp4_last_kernel",
     "nvfp4_shutdown", "nvfp4_last_error", "nvfp4_version", "nvfp4_plan_units", "nvfp4_gemm_static_scratch",
     "nvfp4_interleave_column_blocks", "nvfp4_permute_scales", "nvfp4_gemm_allgather", "nvfp4_quantize", "nvfp4_copy_2d", "nvfp4_copy_column_blocks",
+    "nvfp4_unpermute_scales", "nvfp4_compare_scale_layouts",
 )
 
 
@@ -71,6 +72,10 @@ def load() -> ctypes.CDLL:
     lib.nvfp4_interleave_column_blocks.restype = c_int
     lib.nvfp4_gemm_allgather.argtypes = [ctypes.POINTER(Problem), ctypes.POINTER(GemmConfig), ctypes.POINTER(c_void_p), c_int, c_void_p]
     lib.nvfp4_gemm_allgather.restype = c_int
+    lib.nvfp4_unpermute_scales.argtypes = [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int64, c_int64, c_int64, c_void_p]
+    lib.nvfp4_unpermute_scales.restype = c_int
+    lib.nvfp4_compare_scale_layouts.argtypes = [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int64, c_int64, c_int64, c_void_p, c_void_p]
+    lib.nvfp4_compare_scale_layouts.restype = c_int
     lib.nvfp4_copy_column_blocks.argtypes = [ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int32, c_int64, c_int64, c_int32,
                                              c_int64, c_int32, c_void_p]
     lib.nvfp4_copy_column_blocks.restype = c_int

@@ -2,7 +2,8 @@
 //   * interleave_column_blocks: [g][rows][n_local] fp16 (what an all-gather of per-rank column
 //     blocks leaves in memory) -> row-major [rows][g * n_local];
 //   * permute_scales: plain [rows][K/16] scale bytes -> the 512-byte atom layout the tensor-core
-//     GEMM reads (ref.txt:31, s_128t.py:554-562 in the reference project).
+//     GEMM reads (ref.txt:31, s_128t.py:554-562 in the reference project); scales_from_permuted:
+//     the way back, or a comparison of the two forms;
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -100,6 +101,55 @@ __global__ void __launch_bounds__(256) permute_scales_kernel(const uint8_t* __re
         }
         *reinterpret_cast<uint4*>(perm + l * perm_batch_stride + (static_cast<long long>(rb) * atoms_k + kk) * 512 + r32 * 16) =
             make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+// The way back, and the check that the two scale tensors an operator call carries say the same
+// (the reference's kernels silently trust whichever form they read, template.py:11-14): one
+// thread takes 16 bytes of an atom (four rows x four scales) and either writes the four words to
+// the plain layout or compares them with it.  result[0] counts differing scale bytes, result[1]
+// keeps the smallest (l, row, scale column) linear index of one; padding rows are not looked at.
+template <bool COMPARE>
+__global__ void __launch_bounds__(256) scales_from_permuted_kernel(const uint8_t* __restrict__ perm, uint8_t* __restrict__ plain,
+                                                                   int rows, int sf_cols, long long plain_row_stride,
+                                                                   long long plain_batch_stride, long long perm_batch_stride,
+                                                                   int batches, unsigned long long* __restrict__ result) {
+    const int atoms_k = sf_cols / 4;
+    const int row_blocks = (rows + 127) / 128;
+    const long long per_batch = static_cast<long long>(row_blocks) * atoms_k * 32;
+    const long long total = per_batch * batches;
+    unsigned long long bad = 0, first = ~0ull;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int l = static_cast<int>(i / per_batch);
+        long long rem = i - l * per_batch;
+        const int r32 = static_cast<int>(rem % 32);
+        rem /= 32;
+        const int kk = static_cast<int>(rem % atoms_k);
+        const int rb = static_cast<int>(rem / atoms_k);
+        const uint4 v = *reinterpret_cast<const uint4*>(perm + l * perm_batch_stride + (static_cast<long long>(rb) * atoms_k + kk) * 512 + r32 * 16);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int row = rb * 128 + j * 32 + r32;
+            if (row >= rows) continue;
+            uint32_t* word = reinterpret_cast<uint32_t*>(plain + l * plain_batch_stride + row * plain_row_stride + kk * 4);
+            if (!COMPARE) {
+                *word = w[j];
+            } else {
+                uint32_t diff = *word ^ w[j];
+                if (diff) {
+                    const unsigned long long base = (static_cast<unsigned long long>(l) * rows + row) * sf_cols + kk * 4;
+                    const int first_byte = (__ffs(diff) - 1) / 8;
+                    if (base + first_byte < first) first = base + first_byte;
+                    for (int b = 0; b < 4; ++b, diff >>= 8) bad += (diff & 0xFFu) ? 1 : 0;
+                }
+            }
+        }
+    }
+    if (COMPARE && bad) {
+        atomicAdd(result, bad);
+        atomicMin(result + 1, first);
     }
 }
 

@@ -557,6 +557,51 @@ int nvfp4_permute_scales(const void* plain, void* permuted, int32_t rows, int32_
     return NVFP4_OK;
 }
 
+// Shared by the two entry points that read the permuted form.
+static int scales_from_permuted(const void* permuted, void* plain, int32_t rows, int32_t k, int32_t l, int64_t plain_row_stride,
+                                int64_t plain_batch_stride, int64_t permuted_batch_stride, unsigned long long* result, void* stream_v) {
+    if (!plain || !permuted) return fail(NVFP4_ERR_INVALID_ARGUMENT, "plain and permuted must not be NULL");
+    if (rows < 1 || l < 1 || k < 64 || k % 64) return fail(NVFP4_ERR_INVALID_ARGUMENT, "rows, l >= 1 and k a positive multiple of 64 required");
+    if (!aligned(plain, 4) || !aligned(permuted, 16) || plain_row_stride % 4 || plain_row_stride < k / 16)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "plain must be 4-byte aligned with a row stride that is a multiple of 4 and >= k/16; permuted 16-byte aligned");
+    const long long need = static_cast<long long>((rows + 127) / 128) * (k / 64) * 512;
+    if (l > 1 && (permuted_batch_stride < need || permuted_batch_stride % 16 || plain_batch_stride % 4))
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "batch strides too small or misaligned");
+    int dev = 0, sms = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const long long total = need / 16 * l;
+    long long grid = (total + 255) / 256;
+    if (grid > static_cast<long long>(sms) * 16) grid = static_cast<long long>(sms) * 16;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    if (result) {
+        CUDA_TRY(cudaMemsetAsync(result, 0, 8, stream));
+        CUDA_TRY(cudaMemsetAsync(result + 1, 0xFF, 8, stream));
+        scales_from_permuted_kernel<true><<<static_cast<int>(grid), 256, 0, stream>>>(
+            static_cast<const uint8_t*>(permuted), static_cast<uint8_t*>(plain), rows, k / 16, plain_row_stride, plain_batch_stride,
+            permuted_batch_stride, l, result);
+    } else {
+        scales_from_permuted_kernel<false><<<static_cast<int>(grid), 256, 0, stream>>>(
+            static_cast<const uint8_t*>(permuted), static_cast<uint8_t*>(plain), rows, k / 16, plain_row_stride, plain_batch_stride,
+            permuted_batch_stride, l, nullptr);
+    }
+    CUDA_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    return NVFP4_OK;
+}
+
+int nvfp4_unpermute_scales(const void* permuted, void* plain, int32_t rows, int32_t k, int32_t l, int64_t plain_row_stride,
+                           int64_t plain_batch_stride, int64_t permuted_batch_stride, void* stream_v) {
+    return scales_from_permuted(permuted, plain, rows, k, l, plain_row_stride, plain_batch_stride, permuted_batch_stride, nullptr, stream_v);
+}
+
+int nvfp4_compare_scale_layouts(const void* plain, const void* permuted, int32_t rows, int32_t k, int32_t l, int64_t plain_row_stride,
+                                int64_t plain_batch_stride, int64_t permuted_batch_stride, uint64_t* result, void* stream_v) {
+    if (!result || !aligned(result, 8)) return fail(NVFP4_ERR_INVALID_ARGUMENT, "result must be an 8-byte aligned device pointer to two 64-bit words");
+    return scales_from_permuted(permuted, const_cast<void*>(plain), rows, k, l, plain_row_stride, plain_batch_stride, permuted_batch_stride,
+                                reinterpret_cast<unsigned long long*>(result), stream_v);
+}
+
 int nvfp4_copy_column_blocks(void* const* dst_blocks, const void* const* src_blocks, int32_t n_blocks, int64_t row0, int64_t rows,
                              int32_t n_local, int64_t row_stride, int32_t ctas, void* stream_v) {
     if (n_blocks < 1 || n_blocks > 7 || !dst_blocks || !src_blocks) return fail(NVFP4_ERR_INVALID_ARGUMENT, "1..7 blocks required");

@@ -100,6 +100,33 @@ def gemm(data: input_t, tile_n: int = 0, epilogue: int = 0, grid: int = 0, cta_g
     return data[6]
 
 
+def check_scale_layouts(data: input_t) -> None:
+    """Validate that the plain and the permuted scale tensors of one operator call say the same
+    (the harness passes both, template.py:11-14; the GEMM reads the permuted ones, the GEMV the
+    plain ones).  Compared on the device by ``nvfp4_compare_scale_layouts``; synchronises the
+    current stream and raises ValueError naming the first differing scale."""
+    a, b, sfa, sfb, sfa_perm, sfb_perm, _ = data
+    _require_cuda(data)
+    lib = _lib.load()
+    k = 2 * a.shape[1]
+    stream = torch.cuda.current_stream(a.device).cuda_stream
+    result = torch.empty((2, 2), dtype=torch.int64, device=a.device)
+    for i, (name, plain, perm, rows) in enumerate((("sfa", sfa, sfa_perm, a.shape[0]), ("sfb", sfb, sfb_perm, b.shape[0]))):
+        if perm is None:
+            raise ValueError(f"{name}_permuted is missing")
+        _lib.check(lib.nvfp4_compare_scale_layouts(plain.data_ptr(), perm.data_ptr(), rows, k, a.shape[2],
+                                                   plain.stride(0) if rows > 1 else k // 16, _batch_stride(plain),
+                                                   _batch_stride(perm, 5), result[i].data_ptr(), stream))
+    counts = result.cpu()
+    for i, (name, rows) in enumerate((("sfa", a.shape[0]), ("sfb", b.shape[0]))):
+        bad, first = int(counts[i, 0]), int(counts[i, 1])
+        if bad:
+            col = first % (k // 16)
+            row = (first // (k // 16)) % rows
+            batch = first // (k // 16) // rows
+            raise ValueError(f"{name} and {name}_permuted differ in {bad} scale(s); first at row {row}, scale column {col}, batch {batch}")
+
+
 def check_status() -> None:
     """Synchronise the current stream and raise if a kernel reported a timed-out wait."""
     lib = _lib.load()
