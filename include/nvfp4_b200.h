@@ -79,6 +79,13 @@ int nvfp4_gemm(const nvfp4_problem* problem, const nvfp4_gemm_config* cfg, void*
 int nvfp4_gemv(const nvfp4_problem* problem, void* stream);
 
 /*
+ * The same GEMV with the launch shape chosen by the caller (tests, tuning): rows_per_warp 1, 2 or
+ * 4 and warps_per_cta 1, 2 or 4; 0 = this library's choice (what nvfp4_gemv passes).  Every
+ * combination gives bit-identical results: a row is always summed by one warp in the same order.
+ */
+int nvfp4_gemv_config(const nvfp4_problem* problem, int rows_per_warp, int warps_per_cta, void* stream);
+
+/*
  * What custom_kernel(data) calls (template.py:4-25): n == 1 goes to the GEMV, everything
  * else to the GEMM.
  */

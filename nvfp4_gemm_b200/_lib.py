@@ -21,7 +21,7 @@ EXPORTED_SYMBOLS = (
     "nvfp4_selftest_bounded_wait", "nvfp4_scratch_bytes", "nvfp4_launch_count", "nvfp4_last_kernel",
     "nvfp4_shutdown", "nvfp4_last_error", "nvfp4_version", "nvfp4_plan_units", "nvfp4_gemm_static_scratch",
     "nvfp4_interleave_column_blocks", "nvfp4_permute_scales", "nvfp4_gemm_allgather", "nvfp4_quantize", "nvfp4_copy_2d", "nvfp4_copy_column_blocks",
-    "nvfp4_unpermute_scales", "nvfp4_compare_scale_layouts",
+    "nvfp4_unpermute_scales", "nvfp4_compare_scale_layouts", "nvfp4_gemv_config",
 )
 
 
@@ -87,6 +87,8 @@ def load() -> ctypes.CDLL:
     lib.nvfp4_permute_scales.restype = c_int
     lib.nvfp4_gemv.argtypes = [ctypes.POINTER(Problem), c_void_p]
     lib.nvfp4_gemv.restype = c_int
+    lib.nvfp4_gemv_config.argtypes = [ctypes.POINTER(Problem), c_int, c_int, c_void_p]
+    lib.nvfp4_gemv_config.restype = c_int
     lib.nvfp4_matmul.argtypes = [ctypes.POINTER(Problem), c_void_p]
     lib.nvfp4_matmul.restype = c_int
     lib.nvfp4_check_status.argtypes = [c_void_p]

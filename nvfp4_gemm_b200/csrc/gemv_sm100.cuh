@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_nvfp4_kernel(const GemvPara
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int l = blockIdx.y;
-    const int row0 = (blockIdx.x * kGemvWarps + warp) * R;
+    const int row0 = (blockIdx.x * (blockDim.x >> 5) + warp) * R;   // 1, 2 or 4 warps per CTA, each on its own rows
     if (row0 >= p.M) return;
 
     const uint8_t* b_ptr = p.b + l * p.b_batch_stride;

@@ -469,8 +469,14 @@ int nvfp4_gemm_allgather(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, v
     return gemm_impl(p, &cf, c_peers, n_peers, stream_v);
 }
 
-int nvfp4_gemv(const nvfp4_problem* p, void* stream_v) {
+int nvfp4_gemv(const nvfp4_problem* p, void* stream_v) { return nvfp4_gemv_config(p, 0, 0, stream_v); }
+
+int nvfp4_gemv_config(const nvfp4_problem* p, int rows_per_warp, int warps_per_cta, void* stream_v) {
     if (int rc = validate_common(p)) return rc;
+    if (rows_per_warp != 0 && rows_per_warp != 1 && rows_per_warp != 2 && rows_per_warp != 4)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "rows_per_warp must be 0 (auto), 1, 2 or 4");
+    if (warps_per_cta != 0 && warps_per_cta != 1 && warps_per_cta != 2 && warps_per_cta != 4)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "warps_per_cta must be 0 (auto), 1, 2 or 4");
     if (p->n != 1) return fail(NVFP4_ERR_INVALID_ARGUMENT, "the GEMV needs n == 1 (got %d)", p->n);
     if (!p->sfa || !p->sfb) return fail(NVFP4_ERR_INVALID_ARGUMENT, "the GEMV needs the plain scale tensors (sfa, sfb)");
     if (p->k % 64) return fail(NVFP4_ERR_INVALID_ARGUMENT, "k must be a multiple of 64 (got %d)", p->k);
@@ -502,14 +508,24 @@ int nvfp4_gemv(const nvfp4_problem* p, void* stream_v) {
 
     // rows per warp: short rows amortise the vector's dequantisation over four rows, long rows keep
     // more loads in flight with two (measured on 7168 x 2048 x 4 and 7168 x 16384 x 4)
-    const int r = (p->k <= 4096) ? 4 : 2;
-    const int rows_per_cta = kGemvWarps * r;
+    const int r = rows_per_warp ? rows_per_warp : (p->k <= 4096) ? 4 : 2;
+    // warps per CTA: the block scheduler hands out CTAs as SMs free up, so small CTAs even out the
+    // load when there are few rows -- with 4-warp CTAs a 7168-row problem is 6.05 CTAs per SM and
+    // the last eight SMs run a seventh alone.  Keep at least 16 CTAs per SM if the rows allow it.
+    const long long warps_total = static_cast<long long>((p->m + r - 1) / r) * p->l;
+    int w = warps_per_cta;
+    if (w == 0) w = (warps_total / 4 >= 16ll * c->num_sms) ? 4 : (warps_total / 2 >= 16ll * c->num_sms) ? 2 : 1;
+    const int rows_per_cta = w * r;
     dim3 grid((p->m + rows_per_cta - 1) / rows_per_cta, p->l);
-    if (r == 4) gemv_nvfp4_kernel<4><<<grid, kGemvThreads, 0, stream>>>(g);
-    else gemv_nvfp4_kernel<2><<<grid, kGemvThreads, 0, stream>>>(g);
+    if (r == 4) gemv_nvfp4_kernel<4><<<grid, w * 32, 0, stream>>>(g);
+    else if (r == 2) gemv_nvfp4_kernel<2><<<grid, w * 32, 0, stream>>>(g);
+    else gemv_nvfp4_kernel<1><<<grid, w * 32, 0, stream>>>(g);
     CUDA_TRY(cudaGetLastError());
     g_launches.fetch_add(1);
-    t_last_kernel = (r == 4) ? "gemv_warp_r4" : "gemv_warp_r2";
+    static const char* const names[3][3] = {{"gemv_warp_r1_w1", "gemv_warp_r1_w2", "gemv_warp_r1_w4"},
+                                            {"gemv_warp_r2_w1", "gemv_warp_r2_w2", "gemv_warp_r2_w4"},
+                                            {"gemv_warp_r4_w1", "gemv_warp_r4_w2", "gemv_warp_r4_w4"}};
+    t_last_kernel = names[r == 4 ? 2 : r - 1][w == 4 ? 2 : w - 1];
     return NVFP4_OK;
 }
 

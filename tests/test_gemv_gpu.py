@@ -53,3 +53,26 @@ def test_gemv_general_scales_within_tolerance(sub, oracle):
     torch.cuda.synchronize()
     an, bn, san, sbn = oracle.tensors_to_numpy(data)
     assert_close(out, oracle.ref_gemm(an, bn, san, sbn, accumulate="f64"), rtol=1e-3, atol=1e-3, what="gemv general scales")
+
+
+@pytest.mark.parametrize("rows_per_warp", [1, 2, 4])
+@pytest.mark.parametrize("warps_per_cta", [1, 2, 4])
+def test_every_gemv_launch_shape_gives_the_same_bits(sub, oracle, lib, rows_per_warp, warps_per_cta):
+    """Ragged M (not a multiple of rows per CTA), K that is not a multiple of the unrolled stride."""
+    from nvfp4_gemm_b200 import _lib
+    from nvfp4_gemm_b200.inputs import generate_input
+    data = generate_input(131, 1, 4160, 3, 77)
+    data[6].view(torch.int16).fill_(0x7fff)
+    problem = sub.make_problem(data)
+    _lib.check(lib.nvfp4_gemv_config(problem, rows_per_warp, warps_per_cta, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert sub.last_kernel() == f"gemv_warp_r{rows_per_warp}_w{warps_per_cta}"
+    assert_bit_exact(data[6], expected_fp16(oracle, data), what=f"gemv r{rows_per_warp} w{warps_per_cta}")
+
+
+def test_gemv_config_rejects_unknown_launch_shapes(sub, lib):
+    from nvfp4_gemm_b200 import _lib
+    from nvfp4_gemm_b200.inputs import generate_input
+    problem = sub.make_problem(generate_input(128, 1, 256, 1, 1))
+    assert lib.nvfp4_gemv_config(problem, 3, 0, None) == _lib.NVFP4_ERR_INVALID_ARGUMENT
+    assert lib.nvfp4_gemv_config(problem, 0, 8, None) == _lib.NVFP4_ERR_INVALID_ARGUMENT
