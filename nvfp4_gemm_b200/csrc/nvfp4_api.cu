@@ -506,15 +506,16 @@ int nvfp4_gemv_config(const nvfp4_problem* p, int rows_per_warp, int warps_per_c
     g.c_row_stride = p->c_row_stride; g.c_batch_stride = p->c_batch_stride;
     g.M = p->m; g.K = p->k; g.L = p->l;
 
-    // rows per warp: short rows amortise the vector's dequantisation over four rows, long rows keep
-    // more loads in flight with two (measured on 7168 x 2048 x 4 and 7168 x 16384 x 4)
-    const int r = rows_per_warp ? rows_per_warp : (p->k <= 4096) ? 4 : 2;
-    // warps per CTA: the block scheduler hands out CTAs as SMs free up, so small CTAs even out the
-    // load when there are few rows -- with 4-warp CTAs a 7168-row problem is 6.05 CTAs per SM and
-    // the last eight SMs run a seventh alone.  Keep at least 16 CTAs per SM if the rows allow it.
-    const long long warps_total = static_cast<long long>((p->m + r - 1) / r) * p->l;
-    int w = warps_per_cta;
-    if (w == 0) w = (warps_total / 4 >= 16ll * c->num_sms) ? 4 : (warps_total / 2 >= 16ll * c->num_sms) ? 2 : 1;
+    // Rows per warp: short rows amortise the vector's dequantisation over four rows; long rows keep
+    // more loads in flight with two, or with one when there are so few rows that two per warp
+    // would leave warps short.  One warp per CTA: the block scheduler hands out CTAs as SMs free
+    // up, so the smallest CTAs even out the tail.  Measured on B200 over all nine combinations
+    // (graph replay, cold inputs): 7168 x 16384 x 1: r1/w1 15.5 us, r2/w4 16.3; 7168 x 16384 x 4:
+    // r2/w1 45.2, r2/w4 45.7, r1 49.9; 4096 x 7168 x 8: r2/w1 26.2, r4 27.8; 7168 x 2048 x 4:
+    // r4/w1 9.1, r2 10.1, r1 14.4.
+    const long long rows_total = static_cast<long long>(p->m) * p->l;
+    const int r = rows_per_warp ? rows_per_warp : (p->k <= 4096) ? 4 : (rows_total <= 8192) ? 1 : 2;
+    const int w = warps_per_cta ? warps_per_cta : 1;
     const int rows_per_cta = w * r;
     dim3 grid((p->m + rows_per_cta - 1) / rows_per_cta, p->l);
     if (r == 4) gemv_nvfp4_kernel<4><<<grid, w * 32, 0, stream>>>(g);
