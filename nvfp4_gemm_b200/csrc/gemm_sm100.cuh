@@ -209,6 +209,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
         ptx::tmem_relinquish<CG>();
         ptx::tc_fence_before();
     }
+    // Kernels of this library are often launched back to back (a decode step is a chain of short
+    // GEMMs): let the next launch's CTAs set up (barriers, TMEM, descriptor prefetch) on SMs this
+    // grid leaves idle or frees, and touch global memory only after everything the stream ordered
+    // before this launch is complete.  Without the launch attribute both are no-ops.
+    ptx::grid_dependency_launch_dependents();
+    ptx::grid_dependency_wait();
     if (warp != 0) {
         ptx::named_bar_sync(3, kGemmThreads - 32);
         ptx::tc_fence_after();

@@ -73,6 +73,13 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
     return ok != 0;
 }
 
+// Programmatic dependent launch.  launch_dependents: the next kernel in the stream (if it was
+// launched with programmatic stream serialisation) may be scheduled once every CTA of this grid
+// has said so or exited.  wait: everything the stream ordered before this grid has completed
+// and its memory is visible; a grid launched without the attribute passes straight through.
+__device__ __forceinline__ void grid_dependency_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Bounded wait.  Returns false when the limit ran out or another thread of the CTA already
 // gave up.  The limit is in SM clock cycles and is only consulted every 256 failed polls, so
 // the common case (the barrier completes within a few polls) costs nothing but the polls.
