@@ -428,6 +428,24 @@ def bench_column_parallel(args, w, rank, world, dev, ClockSampler, measured_peak
     gemm_ms = torch.tensor([g0.elapsed_time(g1) / 5], device=dev)
     dist.all_reduce(gemm_ms, op=dist.ReduceOp.MAX)
 
+    # The same whole job on ONE GPU of this box (rank 0, the others idle): the strong-scaling
+    # denominator, measured beside the multi-GPU number.
+    one_gpu_ms = None
+    if rank == 0:
+        del local, gemm_only_c
+        whole = [generate_input(m, n, k, 1, 1111 + i, device=dev) for i in range(2)]
+        for d in whole:
+            S.custom_kernel(d)
+        torch.cuda.synchronize()
+        g0.record()
+        for i in range(6):
+            S.custom_kernel(whole[i % 2])
+        g1.record()
+        torch.cuda.synchronize()
+        one_gpu_ms = g0.elapsed_time(g1) / 6
+        del whole
+    dist.barrier()
+
     if rank == 0:
         ms_per_step = float(ms.item()) / args.steps
         flops = algorithmic_flops(w)
@@ -447,6 +465,8 @@ def bench_column_parallel(args, w, rank, world, dev, ClockSampler, measured_peak
                                              f"column-parallel over N on {world} GPUs, NCCL all-gather of fp16 blocks, {panels} row panels, {mode}"),
                                 timing="CUDA events, max over ranks; 2 rotating input sets (302 MB per rank set) > L2",
                                 gemm_only_ms_per_rank=float(gemm_ms.item()),
+                                one_gpu_same_job_ms=one_gpu_ms,
+                                speedup_over_one_gpu=(one_gpu_ms / ms_per_step) if one_gpu_ms else None,
                                 gemm_only_tflops_per_gpu=flops / world / (float(gemm_ms.item()) * 1e-3) / 1e12,
                                 allgather_bytes_in_per_gpu=gather_bytes, parity_vs_oracle=parity,
                                 nvlink_bound_ms=gather_bytes / 770e9 * 1e3),
