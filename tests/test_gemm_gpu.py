@@ -146,3 +146,45 @@ def test_prefill_shape_full_size_sampled(sub, oracle):
     want = bq @ aq
     have = out[:, torch.from_numpy(cols[:64]).cuda(), 0].double().sum(dim=0).cpu().numpy()
     np.testing.assert_allclose(have, want, rtol=2e-3, atol=2000.0)  # 4096 fp16-rounded addends of magnitude ~1e4 per column
+
+
+def test_back_to_back_launches_respect_stream_order(sub, oracle, lib):
+    """The GEMM is launched with programmatic stream serialisation, so its set-up may overlap the
+    kernel before it.  Its inputs and output must still behave as if the launches ran one after
+    the other: (1) a producer kernel (the quantiser) rewrites A and its scales in place right
+    before each GEMM, with no synchronisation in between; (2) consecutive GEMMs write the same C."""
+    from nvfp4_gemm_b200 import _lib
+    from nvfp4_gemm_b200.inputs import FP4_DTYPE, SF_DTYPE, generate_input
+    m, n, k = 128, 1024, 4096                          # a cluster split-K decode shape
+    stream = torch.cuda.current_stream().cuda_stream
+    base = generate_input(m, n, k, 1, 5)
+    g = torch.Generator().manual_seed(3)
+    xs = [(torch.randn((m, k), generator=g) * (i + 1)).half().cuda() for i in range(4)]
+    packed = torch.zeros((m, k // 2), dtype=torch.uint8, device="cuda")
+    sf = torch.zeros((m, k // 16), dtype=torch.uint8, device="cuda")
+    perm = torch.zeros((k // 64 * 512,), dtype=torch.uint8, device="cuda")
+    a = packed.view(1, m, k // 2).permute(1, 2, 0).view(FP4_DTYPE)
+    sfa = sf.view(1, m, k // 16).permute(1, 2, 0).view(SF_DTYPE)
+    sfa_perm = perm.view(1, 1, k // 64, 32, 4, 4).permute(3, 4, 1, 5, 2, 0).view(SF_DTYPE)
+    outs = [torch.empty((1, m, n), dtype=torch.float16, device="cuda").permute(1, 2, 0) for _ in xs]
+    shared_c = torch.empty((1, m, n), dtype=torch.float16, device="cuda").permute(1, 2, 0)
+    for x, c in zip(xs, outs):                         # no synchronisation inside this loop
+        _lib.check(lib.nvfp4_quantize(x.data_ptr(), 0, packed.data_ptr(), sf.data_ptr(), perm.data_ptr(), m, k, x.stride(0), k // 2,
+                                      k // 16, stream))
+        sub.custom_kernel((a, base[1], sfa, base[3], sfa_perm, base[5], c))
+        sub.custom_kernel((a, base[1], sfa, base[3], sfa_perm, base[5], shared_c))
+    torch.cuda.synchronize()
+    sub.check_status()
+    assert sub.last_kernel().startswith("gemm_splitk")
+    # the same launches again, each waited for before the next: the kernels are deterministic, so
+    # any difference means a launch saw another launch's inputs or was overwritten out of order
+    for i, (x, c) in enumerate(zip(xs, outs)):
+        _lib.check(lib.nvfp4_quantize(x.data_ptr(), 0, packed.data_ptr(), sf.data_ptr(), perm.data_ptr(), m, k, x.stride(0), k // 2,
+                                      k // 16, stream))
+        torch.cuda.synchronize()
+        exp = torch.empty_like(c)
+        sub.custom_kernel((a, base[1], sfa, base[3], sfa_perm, base[5], exp))
+        torch.cuda.synchronize()
+        assert torch.equal(c.view(torch.int16), exp.view(torch.int16)), f"launch {i} read inputs of another launch"
+        assert not torch.equal(exp.view(torch.int16), outs[(i + 1) % len(outs)].view(torch.int16))   # the inputs do differ
+    assert torch.equal(shared_c.view(torch.int16), outs[-1].view(torch.int16))
