@@ -302,7 +302,10 @@ def main():
     roofline["traffic"] = NCU_DRAM_BYTES_PER_LAUNCH.get(wl_key)
 
     line = dict(metric="nvfp4_matmul_throughput", value=tflops, unit="TFLOP/s", n_gpus=1, steps=args.steps,
-                warmup=args.warmup, ms_per_step=ms_per_step, higher_is_better=True, scaling="weak", vs_baseline=None,
+                warmup=args.warmup, ms_per_step=ms_per_step, higher_is_better=True, scaling="weak",
+                # against the fastest time the reference project published for this shape on a B200:
+                # its cuBLASLt submission, 22.6 us (out_cub.txt:16-18); its own kernels took 144 and 459 us
+                vs_baseline=(tflops / (flops / 22.6e-6 / 1e12)) if wl_key == "c1" else None,
                 dtype="e2m1 x ue4m3 -> f32 -> f16", data="synthetic",
                 config=dict(workload=w["name"], timing=f"CUDA events around a CUDA-graph replay of the K steps, median of 5; {n_sets} rotating input sets = {n_sets * set_bytes / 1e6:.0f} MB > L2 {l2_bytes / 1e6:.0f} MB",
                             us_per_step=ms_per_step * 1e3, us_per_step_best_of_5=per_launch_ms[0] * 1e3, gb_per_s=gbs,
