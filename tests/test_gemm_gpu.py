@@ -188,3 +188,37 @@ def test_back_to_back_launches_respect_stream_order(sub, oracle, lib):
         assert torch.equal(c.view(torch.int16), exp.view(torch.int16)), f"launch {i} read inputs of another launch"
         assert not torch.equal(exp.view(torch.int16), outs[(i + 1) % len(outs)].view(torch.int16))   # the inputs do differ
     assert torch.equal(shared_c.view(torch.int16), outs[-1].view(torch.int16))
+
+
+def _padded_like(t, pad_bytes):
+    """The same [rows, cols, L] values inside a wider allocation: row stride cols + pad, batch
+    stride rows * (cols + pad) + pad (element size 1 byte; fp16 for c is handled by the caller)."""
+    rows, cols, l = t.shape
+    raw = t.view(torch.uint8) if t.element_size() == 1 else t
+    row_stride = cols + pad_bytes
+    batch_stride = rows * row_stride + pad_bytes
+    if raw.dtype == torch.uint8:
+        store = torch.full((l * batch_stride + pad_bytes,), 0x5A, dtype=torch.uint8, device=t.device)
+    else:   # fp16 output: a NaN bit pattern no result can have marks the padding
+        store = torch.full((l * batch_stride + pad_bytes,), 0x7E01, dtype=torch.int16, device=t.device).view(torch.float16)
+    view = torch.as_strided(store, (rows, cols, l), (row_stride, 1, batch_stride))
+    view.copy_(raw)
+    return view.view(t.dtype) if t.element_size() == 1 else view
+
+
+@pytest.mark.parametrize("shape", [(300, 512, 1024, 2), (128, 1024, 4096, 1), (64, 1, 2048, 3)])
+def test_operands_and_output_with_padded_strides(sub, oracle, shape):
+    """Rows and batches that are not densely packed (views into wider buffers): the strides of the
+    C ABI's problem description are honoured by the tensor maps, the GEMV's pointers and the stores."""
+    from nvfp4_gemm_b200.inputs import generate_input
+    m, n, k, l = shape
+    a, b, sfa, sfb, sfa_perm, sfb_perm, c = generate_input(m, n, k, l, 21)
+    data = (_padded_like(a, 64), _padded_like(b, 32), _padded_like(sfa, 16), _padded_like(sfb, 8), sfa_perm, sfb_perm, _padded_like(c, 24))
+    data[6].fill_(1.0)
+    out = sub.custom_kernel(data)
+    torch.cuda.synchronize()
+    sub.check_status()
+    assert_bit_exact(out, expected_fp16(oracle, (a, b, sfa, sfb, sfa_perm, sfb_perm, c)), what=f"padded strides {shape}")
+    store = data[6].untyped_storage()
+    whole = torch.empty(0, dtype=torch.int16, device="cuda").set_(store)
+    assert int((whole == 0x7E01).sum().item()) == whole.numel() - m * n * l       # nothing outside C was written
