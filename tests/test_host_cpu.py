@@ -106,3 +106,22 @@ def test_work_partition_covers_every_unit_once_and_is_balanced(lib, total, grid,
     assert max(sizes) - min(sizes) <= 1            # stream-K balance
     assert len(slots) == grid                      # no two workers share a partial-tile slot
     assert lib.nvfp4_plan_units(total, grid, grid, ctypes.byref(b), ctypes.byref(e), None, kt) == _lib.NVFP4_ERR_INVALID_ARGUMENT
+
+
+def test_bench_roofline_arithmetic_matches_the_stated_work():
+    """Algorithmic flops / bytes per launch that bench.py divides by the measured time: the
+    figures of the task's configurations (2*M*N*K*L and the packed operand, scale and output bytes)."""
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location("bench", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    w = bench.WORKLOADS
+    assert bench.algorithmic_flops(w["c1"]) == 30_064_771_072 and bench.algorithmic_bytes(w["c1"]) == 69_074_944
+    assert bench.algorithmic_flops(w["c2"]) == 939_524_096 and bench.algorithmic_bytes(w["c2"]) == 264_335_360
+    assert bench.algorithmic_flops(w["c3"]) == 420_906_795_008 and bench.algorithmic_bytes(w["c3"]) == 104_136_704
+    assert bench.algorithmic_flops(w["c4"]) == 3_848_290_697_216
+    for key, shape in bench.LEADERBOARD.items():
+        assert shape["sol_us"] > 0
+        if "m" in shape:
+            assert shape["k"] % 64 == 0 and (shape["n"] == 1 or shape["n"] % 128 == 0)
