@@ -27,6 +27,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WORKLOADS = {
+    "c0": dict(m=128, n=256, k=256, l=1, bound="hbm", name="C0 CPU-runnable GEMM m128 n256 k256 l1"),
     "c1": dict(m=128, n=7168, k=16384, l=1, bound="hbm", name="C1 decode GEMM m128 n7168 k16384 l1"),
     "c2": dict(m=7168, n=1, k=16384, l=4, bound="hbm", name="C2 GEMV m7168 k16384 l4"),
     "c3": dict(m=4096, n=7168, k=7168, l=1, bound="tensor", name="C3 prefill GEMM m4096 n7168 k7168 l1"),
@@ -112,54 +113,81 @@ class ClockSampler:
         return dict(sm_mhz=(sm[len(sm) // 2] if sm else None), sm_max_mhz=mx, reasons=sorted(reasons), samples=len(sm))
 
 
+class CpuSample:
+    """A bounded slice of a workload for the CPU oracle (C restatement; the reference has no CPU
+    code for this path): all K, the first `rows` rows of A against the first `cols` rows of B,
+    with `cols` wide enough that every host thread gets a 64-column panel of its own.  Inputs are
+    generated once, outside anything that is timed."""
+
+    def __init__(self, w, threads=0):
+        from nvfp4_gemm_b200.inputs import generate_input
+        from oracle import nvfp4_oracle as O
+        O.build_c()
+        self.O = O
+        self.cores = threads or O.c_max_threads()
+        k, n_full = w["k"], w["n"]
+        if n_full > 1:
+            self.rows = min(w["m"], 128)
+            self.cols = min(n_full, max(256, 64 * self.cores))
+        else:                                  # GEMV: one B row; the oracle's panels are over B rows, so one thread works
+            self.rows, self.cols = min(w["m"], 2048), 1
+        self.k, self.n_full = k, n_full
+        self.threads_used = max(1, min(self.cores, -(-self.cols // 64)))
+        data = generate_input(self.rows, self.cols, k, 1, 1111, device="cpu")
+        self.args = O.tensors_to_numpy(data)
+        self.flops = 2.0 * self.rows * self.cols * k
+
+    def run_once(self, threads=None):
+        t0 = time.perf_counter()
+        self.O.ref_gemm_c(*self.args, threads=threads or self.cores)
+        return time.perf_counter() - t0
+
+    def describe(self, reps):
+        return (f"{self.rows}x{self.cols}x{self.k} slice of the workload (all K, first {self.cols} of {self.n_full} B rows), "
+                f"{reps} repeats, {self.threads_used} threads busy")
+
+
 def cpu_baseline_sample(w, threads=0, budget_s=12.0):
-    """Times the CPU oracle (C restatement; the reference has no CPU code for this path) on a
-    bounded slice of the workload: all of A against the first `cols` rows of B."""
-    import numpy as np
-    from nvfp4_gemm_b200.inputs import generate_input
-    from oracle import nvfp4_oracle as O
-    O.build_c()
-    cores = threads or O.c_max_threads()
-    m, k = min(w["m"], 128), w["k"]
-    n_full = w["n"]
-    # ~0.2 GFLOP/s/core lower bound is far too pessimistic; start small and grow to the budget
-    cols = min(n_full, 256) if n_full > 1 else 1
-    rows = m if n_full > 1 else min(w["m"], 2048)
-    data = generate_input(rows, cols, k, 1, 1111, device="cpu")
-    a, b, sfa, sfb = O.tensors_to_numpy(data)
-    t0 = time.perf_counter()
-    O.ref_gemm_c(a, b, sfa, sfb, threads=cores)
-    dt = time.perf_counter() - t0
+    s = CpuSample(w, threads)
+    dt = s.run_once()
     reps = int(max(1, min(20, budget_s / max(dt, 1e-3))))
-    t0 = time.perf_counter()
-    for _ in range(reps):
-        O.ref_gemm_c(a, b, sfa, sfb, threads=cores)
-    dt = (time.perf_counter() - t0) / reps
-    flops = 2.0 * rows * cols * k
-    return dict(tflops=flops / dt / 1e12, seconds=dt, cores=cores,
-                sample=f"{rows}x{cols}x{k} slice of the workload (all K, first {cols} of {n_full} B rows), {reps} repeats")
+    dt = sum(s.run_once() for _ in range(reps)) / reps
+    return dict(tflops=s.flops / dt / 1e12, seconds=dt, cores=s.threads_used, sample=s.describe(reps))
+
+
+def cpu_config0_row():
+    """Config 0 (the CPU-runnable 128 x 256 x 256 GEMM) on the host: all threads and one thread."""
+    s = CpuSample(WORKLOADS["c0"])
+    s.run_once()
+    reps = 50
+    t_all = min(s.run_once() for _ in range(reps))
+    t_one = min(s.run_once(threads=1) for _ in range(reps))
+    return dict(us=t_all * 1e6, threads=s.threads_used, us_one_thread=t_one * 1e6, gflops=s.flops / t_all / 1e9,
+                gflops_one_thread=s.flops / t_one / 1e9, kind="port", timing="best of 50, time.perf_counter around the C oracle call")
 
 
 def run_reference_arm(args, w):
     """The 'reference' arm: the path's CPU implementation on the host cores.  The reference has no
-    CPU code (and its harness ref_kernel is absent), so this is the oracle port."""
+    CPU code (and its harness ref_kernel is absent), so this is the oracle port.  A step is one
+    pass over the bounded slice; inputs are generated before anything is timed."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    vals = []
+    s = CpuSample(w)
+    # size the sample so that warm-up + K steps end within about two minutes
+    while s.run_once() * (args.steps + args.warmup) > 120.0 and s.rows > 8:
+        s = CpuSample(dict(w, m=s.rows // 2))
     for _ in range(args.warmup):
-        cpu_baseline_sample(w, budget_s=0.5)
-    info = None
-    t_all = time.perf_counter()
-    for _ in range(args.steps):
-        info = cpu_baseline_sample(w, budget_s=2.0)
-        vals.append(info["tflops"])
-    value = sum(vals) / len(vals)
+        s.run_once()
+    steps = args.steps
+    times = [s.run_once() for _ in range(steps)]
+    dt = sum(times) / len(times)
+    value = s.flops / dt / 1e12
     line = dict(impl="reference", metric="nvfp4_matmul_throughput", value=value, unit="TFLOP/s", n_gpus=args.gpus,
-                steps=args.steps, warmup=args.warmup, ms_per_step=1e3 * (time.perf_counter() - t_all) / args.steps,
+                steps=steps, warmup=args.warmup, ms_per_step=1e3 * dt,
                 higher_is_better=True, scaling="strong" if args.gpus > 1 else "weak", vs_baseline=None, dtype="e2m1 x ue4m3 -> f32 -> f16",
                 data="synthetic", config=dict(workload=w["name"]),
-                cpu_baseline=dict(value=value, unit="TFLOP/s", cores=info["cores"], kind="port", sample=info["sample"]),
+                cpu_baseline=dict(value=value, unit="TFLOP/s", cores=s.threads_used, kind="port", sample=s.describe(steps)),
                 e2e=dict(value=value, unit="TFLOP/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
     print(json.dumps(line), flush=True)
 
@@ -200,8 +228,7 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
     if world > 1:
-        from nvfp4_gemm_b200.multi_gpu import bench_column_parallel
-        bench_column_parallel(args, w, rank, world, dev, ClockSampler, measured_peaks, algorithmic_flops)
+        bench_column_parallel(args, w, rank, world, dev)
         return
 
     peaks = measured_peaks()
@@ -252,6 +279,7 @@ def main():
         torch.cuda.synchronize()
     S.check_status()
     kernel_name = S.last_kernel()
+    isolated_us = isolated_launch_us(lambda i: step(i), n_sets)
     reps.sort()
     total_ms = reps[len(reps) // 2]                  # median of 5 timed regions of K steps each
     per_launch_ms = [r / args.steps for r in reps]
@@ -309,22 +337,48 @@ def main():
                 dtype="e2m1 x ue4m3 -> f32 -> f16", data="synthetic",
                 config=dict(workload=w["name"], timing=f"CUDA events around a CUDA-graph replay of the K steps, median of 5; {n_sets} rotating input sets = {n_sets * set_bytes / 1e6:.0f} MB > L2 {l2_bytes / 1e6:.0f} MB",
                             us_per_step=ms_per_step * 1e3, us_per_step_best_of_5=per_launch_ms[0] * 1e3, gb_per_s=gbs,
+                            isolated_launch_us=isolated_us,
+                            isolated_launch_timing="one launch between two CUDA events, stream synchronised before each, no graph, inputs rotating (cold L2); median of 60",
                             reference_published_us={"cuBLASLt": 22.6, "cute_dsl_template": 144.0, "hand_written_tcgen05": 459.0} if wl_key == "c1" else None),
                 roofline=roofline,
                 e2e=dict(value=flops / (e2e_ms * 1e-3) / 1e12, unit="TFLOP/s", ms_per_step=e2e_ms, h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
                 gpu_launches=int(launches), clocks=clocks)
 
     if not args.no_extra:
-        line["other_configs"] = extra_table(S, generate_input, dev, peaks)
+        del sets, host_sets, dev_buf
+        torch.cuda.empty_cache()
+        line["other_configs"] = extra_table(S, generate_input, dev, peaks, local_rank)
     if not args.no_cpu_baseline:
         cb = cpu_baseline_sample(w)
         line["cpu_baseline"] = dict(value=cb["tflops"], unit="TFLOP/s", cores=cb["cores"], kind="port", sample=cb["sample"])
+        if not args.no_extra:
+            line["other_configs"]["c0_cpu_128x256x256"] = cpu_config0_row()
     print(json.dumps(line), flush=True)
 
 
-def extra_table(S, generate_input, dev, peaks):
+def isolated_launch_us(fn, n_sets, n=60):
+    """Latency one launch sees on its own: events around a single call, the stream drained before
+    each, no CUDA graph (so no overlap with a neighbouring launch), inputs rotating through more
+    than L2.  Includes the launch overhead a lone call pays."""
+    import torch
+    ts = []
+    for i in range(n + 5):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn(i % n_sets)
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= 5:
+            ts.append(e0.elapsed_time(e1) * 1e3)
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def extra_table(S, generate_input, dev, peaks, gpu_index):
     """Device-timed µs / TFLOPS / GB/s for the other single-GPU configurations and the same-GPU
-    cuBLASLt comparator (torch._scaled_mm), reported beside the headline line."""
+    cuBLASLt comparator (torch._scaled_mm), reported beside the headline line.  Every row carries
+    the SM clock sampled while that row's kernels ran."""
     import torch
     out = {}
 
@@ -342,42 +396,60 @@ def extra_table(S, generate_input, dev, peaks):
         torch.cuda.synchronize()
         g.replay()
         torch.cuda.synchronize()
-        best = None
-        for _ in range(5):
+        ts = []
+        for _ in range(7):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             g.replay()
             e1.record()
             torch.cuda.synchronize()
-            t = e0.elapsed_time(e1) / (inner * n_sets) * 1e3
-            best = t if best is None or t < best else best
-        return best
+            ts.append(e0.elapsed_time(e1) / (inner * n_sets) * 1e3)
+        # keep the row's load up long enough for the clock sampler (100 ms period) to see it
+        t0 = time.perf_counter()
+        while time.perf_counter() - t0 < 0.35:
+            g.replay()
+            torch.cuda.synchronize()
+        ts.sort()
+        return ts[0], ts[len(ts) // 2]
 
     def flat(t):
         return torch.as_strided(t.view(torch.uint8), (t.numel(),), (1,)).view(t.dtype)
 
     shapes = {key: WORKLOADS[key] for key in ("c1", "c2", "c3")}
     shapes.update({key: v for key, v in LEADERBOARD.items() if "m" in v})
+    shapes["c4_one_gpu"] = WORKLOADS["c4"]
     for key, w in shapes.items():
         # enough rotating input sets to exceed 3x L2 (126 MB), so every launch reads HBM
-        n_sets = int(min(48, max(3, -(-400e6 // algorithmic_bytes(w)))))
+        n_sets = int(min(48, max(2 if key == "c4_one_gpu" else 3, -(-400e6 // algorithmic_bytes(w)))))
         sets = [generate_input(w["m"], w["n"], w["k"], w["l"], 2000 + i, device=dev) for i in range(n_sets)]
-        us = time_fn(lambda i: S.custom_kernel(sets[i % n_sets]), n_sets)
-        rec = dict(us=us, tflops=algorithmic_flops(w) / us / 1e6, gb_per_s=algorithmic_bytes(w) / us / 1e3, kernel=S.last_kernel())
+        sampler = ClockSampler(gpu_index)
+        sampler.start()
+        us, us_median = time_fn(lambda i: S.custom_kernel(sets[i % n_sets]), n_sets, inner=2 if key == "c4_one_gpu" else 4)
+        clk = sampler.stop()
+        rec = dict(us=us, us_median=us_median, tflops=algorithmic_flops(w) / us / 1e6, gb_per_s=algorithmic_bytes(w) / us / 1e3, kernel=S.last_kernel())
         rec["frac_hbm_measured"] = rec["gb_per_s"] / peaks["hbm_gbs"]
         rec["frac_fp4_nominal"] = rec["tflops"] / FP4_DENSE_PEAK_TFLOPS
         rec["input_sets"] = n_sets
+        rec["clocks"] = dict(sm_mhz=clk.get("sm_mhz"), reasons=clk.get("reasons"), samples=clk.get("samples"))
         sol = LEADERBOARD.get(key, w).get("sol_us")
         if sol:
             rec["task_sol_us_at_1500mhz"] = sol
             rec["sol_over_measured"] = sol / us
+        if w["m"] <= 128 and w["n"] > 1:
+            rec["isolated_launch_us"] = isolated_launch_us(lambda i: S.custom_kernel(sets[i % n_sets]), n_sets)
         if w["n"] > 1:
             try:
                 ar = [(s[0][:, :, 0], s[1][:, :, 0].t(), flat(s[4]), flat(s[5])) for s in sets]
                 outs = [torch.empty((w["m"], w["n"]), dtype=torch.float16, device=dev) for _ in sets]
-                cus = time_fn(lambda i: torch._scaled_mm(*ar[i % n_sets], out_dtype=torch.float16, out=outs[i % n_sets]), n_sets)
+                cus, cus_median = time_fn(lambda i: torch._scaled_mm(*ar[i % n_sets], out_dtype=torch.float16, out=outs[i % n_sets]), n_sets,
+                                          inner=2 if key == "c4_one_gpu" else 4)
                 rec["cublaslt_us"] = cus
+                rec["cublaslt_us_median"] = cus_median
                 rec["cublaslt_tflops"] = algorithmic_flops(w) / cus / 1e6
+                if w["m"] <= 128:
+                    rec["cublaslt_isolated_launch_us"] = isolated_launch_us(
+                        lambda i: torch._scaled_mm(*ar[i % n_sets], out_dtype=torch.float16, out=outs[i % n_sets]), n_sets)
+                del ar, outs
             except Exception as e:  # noqa: BLE001
                 rec["cublaslt_us"] = None
                 rec["cublaslt_error"] = str(e)[:200]
@@ -386,6 +458,158 @@ def extra_table(S, generate_input, dev, peaks):
         torch.cuda.empty_cache()
     S.check_status()
     return out
+
+
+def bench_column_parallel(args, w, rank, world, dev):
+    """`bench.py --gpus N` for N > 1: strong scaling of the one partitioned workload."""
+    import torch
+    import torch.distributed as dist
+    from nvfp4_gemm_b200 import submission as S
+    from nvfp4_gemm_b200.inputs import generate_input
+    from nvfp4_gemm_b200.multi_gpu import (ColumnParallelGemm, CopyEngineAllGatherGemm, FusedAllGatherGemm, PanelAllGatherGemm,
+                                           best_allgather_mode, plan_shard, shard_inputs, to_device_same_layout)
+
+    m, n, k = w["m"], w["n"], w["k"]
+    shard = plan_shard(n, world, rank)
+    # every rank builds the same full B from the seed and keeps its rows (inputs are synthetic)
+    n_sets = 2
+    sets = []
+    for i in range(n_sets):
+        full = generate_input(m, n, k, 1, 1111 + i, device="cpu")
+        local = shard_inputs(full, shard)
+        sets.append(tuple(to_device_same_layout(t, dev) if j < 6 else None for j, t in enumerate(local)))
+        del full
+    mode = getattr(args, "allgather", "auto")
+    if mode == "auto":
+        mode = best_allgather_mode(world)
+    fused = None
+    panels = max(1, int(getattr(args, "panels", 4)))
+    try:
+        if mode == "fused":
+            fused = FusedAllGatherGemm(m, n, k, device=dev)
+        elif mode == "ce":
+            fused = CopyEngineAllGatherGemm(m, n, k, device=dev, panels=panels)
+        elif mode in ("pull", "push"):
+            fused = PanelAllGatherGemm(m, n, k, device=dev, panels=panels, direction=mode)
+    except Exception as e:  # symmetric memory unavailable on this box: use the NCCL path and say so
+        mode = f"nccl ({mode} path unavailable: {str(e)[:120]})"
+    if fused is not None:
+        c_full = [fused.c_full]
+
+        def step(i):
+            fused(sets[i % n_sets])
+    else:
+        c_full = [torch.empty((1, m, n), dtype=torch.float16, device=dev).permute(1, 2, 0)]
+        plan = ColumnParallelGemm(m, n, k, device=dev, panels=panels)
+
+        def step(i):
+            plan(sets[i % n_sets], c_full[0])
+
+    for i in range(args.warmup):
+        step(i)
+    S.check_status()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+
+    parity = None
+    step(0)                      # every rank takes part in the collective; rank 0 then checks the result
+    torch.cuda.synchronize()
+    if rank == 0:
+        # sampled rows of the gathered result against the CPU oracle (all N columns, so every
+        # rank's block and the re-layout are covered)
+        import numpy as np
+        from oracle import nvfp4_oracle as O
+        full = generate_input(m, n, k, 1, 1111, device="cpu")
+        rows = np.sort(np.random.default_rng(0).choice(m, 16, replace=False))
+        a_np, b_np, sfa_np, sfb_np = O.tensors_to_numpy(full)
+        exp = O.ref_gemm_c(a_np[rows], b_np, sfa_np[rows], sfb_np)
+        got = c_full[0][torch.from_numpy(rows).to(dev)].cpu().numpy()
+        parity = "bit-exact on 16 sampled rows x all columns" if np.array_equal(got.view(np.uint16), exp.view(np.uint16)) else "MISMATCH"
+        del full
+    dist.barrier()
+
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    launches0 = S.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    launches = S.launch_count() - launches0
+    clocks = sampler.stop()
+    S.check_status()
+
+    # GEMM-only time of this rank's block, for the split of compute vs exchange
+    torch.cuda.synchronize()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    gemm_only_c = torch.empty((1, m, shard.n_local), dtype=torch.float16, device=dev).permute(1, 2, 0)
+    local = sets[0][:6] + (gemm_only_c,)
+    S.custom_kernel(local)
+    g0.record()
+    for _ in range(5):
+        S.custom_kernel(local)
+    g1.record()
+    torch.cuda.synchronize()
+    gemm_ms = torch.tensor([g0.elapsed_time(g1) / 5], device=dev)
+    dist.all_reduce(gemm_ms, op=dist.ReduceOp.MAX)
+
+    # The same whole job on ONE GPU of this box (rank 0, the others idle): the strong-scaling
+    # denominator, measured beside the multi-GPU number.
+    one_gpu_ms = None
+    if rank == 0:
+        del local, gemm_only_c
+        whole = [generate_input(m, n, k, 1, 1111 + i, device=dev) for i in range(2)]
+        for d in whole:
+            S.custom_kernel(d)
+        torch.cuda.synchronize()
+        g0.record()
+        for i in range(6):
+            S.custom_kernel(whole[i % 2])
+        g1.record()
+        torch.cuda.synchronize()
+        one_gpu_ms = g0.elapsed_time(g1) / 6
+        del whole
+    dist.barrier()
+
+    if rank == 0:
+        ms_per_step = float(ms.item()) / args.steps
+        flops = algorithmic_flops(w)
+        tflops = flops / (ms_per_step * 1e-3) / 1e12
+        gather_bytes = (world - 1) / world * m * n * 2
+        line = dict(metric="nvfp4_matmul_throughput", value=tflops, unit="TFLOP/s", n_gpus=world, steps=args.steps,
+                    warmup=args.warmup, ms_per_step=ms_per_step, higher_is_better=True, scaling="strong", vs_baseline=None,
+                    dtype="e2m1 x ue4m3 -> f32 -> f16", data="synthetic",
+                    config=dict(workload=w["name"], parallelism=(f"column-parallel over N on {world} GPUs; column blocks pushed to the peers by copy engine per row panel, overlapping the next panel's GEMM"
+                                             if mode == "ce" else
+                                             f"column-parallel over N on {world} GPUs; each rank pulls the other ranks' column blocks per row panel with its own copy kernel (loads over NVLink), overlapping the next panel's GEMM"
+                                             if mode == "pull" else
+                                             f"column-parallel over N on {world} GPUs; each rank pushes its column block to the peers per row panel ({panels} panels) with its own copy kernel (stores over NVLink), overlapping the next panel's GEMM"
+                                             if mode == "push" else
+                                             f"column-parallel over N on {world} GPUs; all-gather fused into the GEMM epilogue (peer stores over NVLink)"
+                                             if fused is not None else
+                                             f"column-parallel over N on {world} GPUs, NCCL all-gather of fp16 blocks, {panels} row panels, {mode}"),
+                                timing="CUDA events, max over ranks; 2 rotating input sets (302 MB per rank set) > L2",
+                                gemm_only_ms_per_rank=float(gemm_ms.item()),
+                                one_gpu_same_job_ms=one_gpu_ms,
+                                speedup_over_one_gpu=(one_gpu_ms / ms_per_step) if one_gpu_ms else None,
+                                gemm_only_tflops_per_gpu=flops / world / (float(gemm_ms.item()) * 1e-3) / 1e12,
+                                allgather_bytes_in_per_gpu=gather_bytes, parity_vs_oracle=parity,
+                                nvlink_bound_ms=gather_bytes / 770e9 * 1e3),
+                    roofline=dict(bound="nvlink", achieved=gather_bytes / (ms_per_step * 1e-3) / 1e9, peak=770.0, unit="GB/s",
+                                  frac=gather_bytes / (ms_per_step * 1e-3) / 1e9 / 770.0, traffic=None,
+                                  peak_source="measured peer copy per direction"),
+                    e2e=dict(value=tflops, unit="TFLOP/s", ms_per_step=ms_per_step, h2d_bytes_per_step=0, d2h_bytes_per_step=0,
+                             note="inputs resident; the gathered fp16 C (all N columns) is the step's result on every rank"),
+                    gpu_launches=int(launches), clocks=clocks)
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -230,6 +230,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
     const uint64_t timeout = p.timeout_cycles;
 #ifdef NVFP4_TRACE
     const long long trace_t_start = clock64();
+    const uint64_t trace_ns_start = ptx::globaltimer_ns();
     long long trace_wait = 0, trace_wait2 = 0;
 #define NVFP4_TRACE_BEGIN() const long long trace_t0 = clock64()
 #define NVFP4_TRACE_END(acc) acc += clock64() - trace_t0
@@ -391,6 +392,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                 p.trace[blockIdx.x * 16 + 2] = trace_wait;
                 p.trace[blockIdx.x * 16 + 3] = trace_wait2;
                 p.trace[blockIdx.x * 16 + 0] = clock64() - trace_t_start;
+                p.trace[blockIdx.x * 16 + 7] = ptx::globaltimer_ns() - trace_ns_start;
             }
 #endif
         }

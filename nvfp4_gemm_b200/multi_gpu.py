@@ -330,152 +330,3 @@ def best_allgather_mode(world: int) -> str:
     and the epilogue's peer stores hide best; from four GPUs on the exchange dominates and the copy
     kernel pushing finished row panels keeps the links fuller than the epilogue does."""
     return "fused" if world <= 2 else "push"
-
-
-def bench_column_parallel(args, w, rank, world, dev, ClockSampler, measured_peaks, algorithmic_flops):
-    """`bench.py --gpus N` for N > 1: strong scaling of the one partitioned workload."""
-    import json
-    from .inputs import generate_input
-    from . import submission as S
-
-    m, n, k = w["m"], w["n"], w["k"]
-    shard = plan_shard(n, world, rank)
-    # every rank builds the same full B from the seed and keeps its rows (inputs are synthetic)
-    n_sets = 2
-    sets = []
-    for i in range(n_sets):
-        full = generate_input(m, n, k, 1, 1111 + i, device="cpu")
-        local = shard_inputs(full, shard)
-        sets.append(tuple(to_device_same_layout(t, dev) if j < 6 else None for j, t in enumerate(local)))
-        del full
-    mode = getattr(args, "allgather", "auto")
-    if mode == "auto":
-        mode = best_allgather_mode(world)
-    fused = None
-    panels = max(1, int(getattr(args, "panels", 4)))
-    try:
-        if mode == "fused":
-            fused = FusedAllGatherGemm(m, n, k, device=dev)
-        elif mode == "ce":
-            fused = CopyEngineAllGatherGemm(m, n, k, device=dev, panels=panels)
-        elif mode in ("pull", "push"):
-            fused = PanelAllGatherGemm(m, n, k, device=dev, panels=panels, direction=mode)
-    except Exception as e:  # symmetric memory unavailable on this box: use the NCCL path and say so
-        mode = f"nccl ({mode} path unavailable: {str(e)[:120]})"
-    if fused is not None:
-        c_full = [fused.c_full]
-
-        def step(i):
-            fused(sets[i % n_sets])
-    else:
-        c_full = [torch.empty((1, m, n), dtype=torch.float16, device=dev).permute(1, 2, 0)]
-        plan = ColumnParallelGemm(m, n, k, device=dev, panels=panels)
-
-        def step(i):
-            plan(sets[i % n_sets], c_full[0])
-
-    for i in range(args.warmup):
-        step(i)
-    S.check_status()
-    torch.cuda.synchronize()
-    dist.barrier()
-    torch.cuda.synchronize()
-
-    parity = None
-    step(0)                      # every rank takes part in the collective; rank 0 then checks the result
-    torch.cuda.synchronize()
-    if rank == 0:
-        # sampled rows of the gathered result against the CPU oracle (all N columns, so every
-        # rank's block and the re-layout are covered)
-        import numpy as np
-        from oracle import nvfp4_oracle as O
-        full = generate_input(m, n, k, 1, 1111, device="cpu")
-        rows = np.sort(np.random.default_rng(0).choice(m, 16, replace=False))
-        a_np, b_np, sfa_np, sfb_np = O.tensors_to_numpy(full)
-        exp = O.ref_gemm_c(a_np[rows], b_np, sfa_np[rows], sfb_np)
-        got = c_full[0][torch.from_numpy(rows).to(dev)].cpu().numpy()
-        parity = "bit-exact on 16 sampled rows x all columns" if np.array_equal(got.view(np.uint16), exp.view(np.uint16)) else "MISMATCH"
-        del full
-    dist.barrier()
-
-    sampler = ClockSampler(dev.index)
-    sampler.start()
-    launches0 = S.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        step(i)
-    e1.record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    launches = S.launch_count() - launches0
-    clocks = sampler.stop()
-    S.check_status()
-
-    # GEMM-only time of this rank's block, for the split of compute vs exchange
-    torch.cuda.synchronize()
-    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    gemm_only_c = torch.empty((1, m, shard.n_local), dtype=torch.float16, device=dev).permute(1, 2, 0)
-    local = sets[0][:6] + (gemm_only_c,)
-    S.custom_kernel(local)
-    g0.record()
-    for _ in range(5):
-        S.custom_kernel(local)
-    g1.record()
-    torch.cuda.synchronize()
-    gemm_ms = torch.tensor([g0.elapsed_time(g1) / 5], device=dev)
-    dist.all_reduce(gemm_ms, op=dist.ReduceOp.MAX)
-
-    # The same whole job on ONE GPU of this box (rank 0, the others idle): the strong-scaling
-    # denominator, measured beside the multi-GPU number.
-    one_gpu_ms = None
-    if rank == 0:
-        del local, gemm_only_c
-        whole = [generate_input(m, n, k, 1, 1111 + i, device=dev) for i in range(2)]
-        for d in whole:
-            S.custom_kernel(d)
-        torch.cuda.synchronize()
-        g0.record()
-        for i in range(6):
-            S.custom_kernel(whole[i % 2])
-        g1.record()
-        torch.cuda.synchronize()
-        one_gpu_ms = g0.elapsed_time(g1) / 6
-        del whole
-    dist.barrier()
-
-    if rank == 0:
-        ms_per_step = float(ms.item()) / args.steps
-        flops = algorithmic_flops(w)
-        tflops = flops / (ms_per_step * 1e-3) / 1e12
-        gather_bytes = (world - 1) / world * m * n * 2
-        line = dict(metric="nvfp4_matmul_throughput", value=tflops, unit="TFLOP/s", n_gpus=world, steps=args.steps,
-                    warmup=args.warmup, ms_per_step=ms_per_step, higher_is_better=True, scaling="strong", vs_baseline=None,
-                    dtype="e2m1 x ue4m3 -> f32 -> f16", data="synthetic",
-                    config=dict(workload=w["name"], parallelism=(f"column-parallel over N on {world} GPUs; column blocks pushed to the peers by copy engine per row panel, overlapping the next panel's GEMM"
-                                             if mode == "ce" else
-                                             f"column-parallel over N on {world} GPUs; each rank pulls the other ranks' column blocks per row panel with its own copy kernel (loads over NVLink), overlapping the next panel's GEMM"
-                                             if mode == "pull" else
-                                             f"column-parallel over N on {world} GPUs; each rank pushes its column block to the peers per row panel ({panels} panels) with its own copy kernel (stores over NVLink), overlapping the next panel's GEMM"
-                                             if mode == "push" else
-                                             f"column-parallel over N on {world} GPUs; all-gather fused into the GEMM epilogue (peer stores over NVLink)"
-                                             if fused is not None else
-                                             f"column-parallel over N on {world} GPUs, NCCL all-gather of fp16 blocks, {panels} row panels, {mode}"),
-                                timing="CUDA events, max over ranks; 2 rotating input sets (302 MB per rank set) > L2",
-                                gemm_only_ms_per_rank=float(gemm_ms.item()),
-                                one_gpu_same_job_ms=one_gpu_ms,
-                                speedup_over_one_gpu=(one_gpu_ms / ms_per_step) if one_gpu_ms else None,
-                                gemm_only_tflops_per_gpu=flops / world / (float(gemm_ms.item()) * 1e-3) / 1e12,
-                                allgather_bytes_in_per_gpu=gather_bytes, parity_vs_oracle=parity,
-                                nvlink_bound_ms=gather_bytes / 770e9 * 1e3),
-                    roofline=dict(bound="nvlink", achieved=gather_bytes / (ms_per_step * 1e-3) / 1e9, peak=770.0, unit="GB/s",
-                                  frac=gather_bytes / (ms_per_step * 1e-3) / 1e9 / 770.0, traffic=None,
-                                  peak_source="measured peer copy per direction"),
-                    e2e=dict(value=tflops, unit="TFLOP/s", ms_per_step=ms_per_step, h2d_bytes_per_step=0, d2h_bytes_per_step=0,
-                             note="inputs resident; the gathered fp16 C (all N columns) is the step's result on every rank"),
-                    gpu_launches=int(launches), clocks=clocks)
-        print(json.dumps(line), flush=True)
-    dist.barrier()
-    dist.destroy_process_group()

@@ -32,18 +32,22 @@ def make_problem(data: input_t) -> Problem:
         raise ValueError(f"c has shape {tuple(c.shape)}, expected {(m, n, l)}")
     if a.stride(1) != 1 or b.stride(1) != 1 or c.stride(1) != 1 and n > 1:
         raise ValueError("a, b must be K-major (stride 1 along k) and c row-major")
-    if a.element_size() != 1 or b.element_size() != 1 or sfa.element_size() != 1 or c.dtype != torch.float16:
+    if a.element_size() != 1 or b.element_size() != 1 or c.dtype != torch.float16 or any(
+            t is not None and t.element_size() != 1 for t in (sfa, sfb, sfa_perm, sfb_perm)):
         raise ValueError("expected packed fp4 (1 byte per 2 values), 1-byte scales and fp16 output")
     p = Problem()
     p.a, p.b, p.c = a.data_ptr(), b.data_ptr(), c.data_ptr()
-    p.sfa, p.sfb = sfa.data_ptr(), sfb.data_ptr()
+    p.sfa = sfa.data_ptr() if sfa is not None else None
+    p.sfb = sfb.data_ptr() if sfb is not None else None
     p.sfa_perm = sfa_perm.data_ptr() if sfa_perm is not None else None
     p.sfb_perm = sfb_perm.data_ptr() if sfb_perm is not None else None
     p.m, p.n, p.k, p.l = m, n, 2 * k_bytes, l
     p.a_row_stride, p.a_batch_stride = a.stride(0), _batch_stride(a)
     p.b_row_stride, p.b_batch_stride = (b.stride(0) if n > 1 else k_bytes), _batch_stride(b)
-    p.sfa_row_stride, p.sfa_batch_stride = sfa.stride(0), _batch_stride(sfa)
-    p.sfb_row_stride, p.sfb_batch_stride = (sfb.stride(0) if n > 1 else k_bytes // 8), _batch_stride(sfb)
+    if sfa is not None:
+        p.sfa_row_stride, p.sfa_batch_stride = sfa.stride(0), _batch_stride(sfa)
+    if sfb is not None:
+        p.sfb_row_stride, p.sfb_batch_stride = (sfb.stride(0) if n > 1 else k_bytes // 8), _batch_stride(sfb)
     # permuted scales: [32, 4, rest_rows, 4, rest_k, L]; the batch is the last dimension
     p.sfa_perm_batch_stride = _batch_stride(sfa_perm, 5) if sfa_perm is not None else 0
     p.sfb_perm_batch_stride = _batch_stride(sfb_perm, 5) if sfb_perm is not None else 0
@@ -59,12 +63,16 @@ def _require_cuda(data: input_t) -> None:
 _problem_cache: dict = {}
 
 
+def _layout_key(t) -> tuple:
+    """Everything of a tensor that make_problem() reads: address, shape and strides (None-safe)."""
+    return (0, (), ()) if t is None else (t.data_ptr(), tuple(t.shape), tuple(t.stride()))
+
+
 def _cached_problem(data: input_t) -> Problem:
     """make_problem() is ~40 attribute reads; harnesses call with the same tensors over and over,
-    so remember the translated struct by the tensors' addresses and shapes."""
-    a, b, _, _, sfa_perm, sfb_perm, c = data
-    key = (a.data_ptr(), b.data_ptr(), c.data_ptr(), sfa_perm.data_ptr(), sfb_perm.data_ptr(), data[2].data_ptr(),
-           data[3].data_ptr(), a.shape, b.shape, c.stride())
+    so remember the translated struct by the address, shape and strides of all seven tensors (a
+    recycled address with another layout is a different key)."""
+    key = tuple(_layout_key(t) for t in data)
     hit = _problem_cache.get(key)
     if hit is None:
         _require_cuda(data)

@@ -4,12 +4,17 @@ Only the test-suite, the smoke check and the bench's CPU-baseline leg may import
 this module; the product path (``nvfp4_gemm_b200``) never does and fails loudly
 when its CUDA library is missing.
 
-PARITY UNPINNED by reference fixtures: the reference repository holds no golden
-vectors, no CPU implementation and no tests for this path, and the harness file
-that defines ``ref_kernel`` (named at task.yml:5 as ``reference.py``) is not part
-of it.  The arithmetic below therefore restates the published definition of the
-operator -- dequantise to fp32, accumulate in fp32, cast to fp16 -- using the
-layout facts the reference does pin:
+PARITY PINNED by outputs of the reference's own code: its cuBLASLt submission
+(sub_cub.py:48-143, bound by custom_kernel at sub_cub.py:165-169) is compiled from the
+reference's source by ``oracle/build_ref.py`` and run on a B200 on this repository's
+seeded inputs -- live in ``tests/test_reference_pin_gpu.py`` and as committed fixtures
+``tests/golden/ref_cublaslt.json`` (config 0, the test shapes of task.yml:41-51 and the
+benchmark shapes of task.yml:53-56), which ``tests/test_oracle_cpu.py`` holds this oracle
+to bit for bit.  The reference holds no golden vectors, no CPU implementation and no tests
+of its own for this path, and the harness file that defines ``ref_kernel`` (named at
+task.yml:5 as ``reference.py``) is not part of it, so the arithmetic below restates the
+published definition of the operator -- dequantise to fp32, accumulate in fp32, cast to
+fp16 -- using the layout facts the reference does pin:
 
 * tensor shapes / dtypes / packing: template.py:9-22, task.yml:18-22
   (``a`` is [M, K/2, L] bytes, two e2m1 nibbles per byte, K-major);
@@ -22,7 +27,7 @@ layout facts the reference does pin:
 * per-16-block semantics (exact block dot product, times sfa*sfb, fp32
   accumulate): old_files/sub_gemm.py:170-174,211-218.
 
-Independent pins used by the tests: torch's own ``float8_e4m3fn -> float32``
+Further pins used by the tests: torch's own ``float8_e4m3fn -> float32``
 conversion for the scale decode, hand-computable known-answer cases, fp64
 re-computation, and (on a GPU) cuBLASLt's block-scaled FP4 matmul, which is the
 library call the reference configures in sub_cub.py:67-133.
