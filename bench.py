@@ -344,6 +344,8 @@ def main():
                 e2e=dict(value=flops / (e2e_ms * 1e-3) / 1e12, unit="TFLOP/s", ms_per_step=e2e_ms, h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
                 gpu_launches=int(launches), clocks=clocks)
 
+    del graph
+    S.release_stream(side)            # the timed graph is gone: give its stream's scratch set back
     if not args.no_extra:
         del sets, host_sets, dev_buf
         torch.cuda.empty_cache()
@@ -410,6 +412,8 @@ def extra_table(S, generate_input, dev, peaks, gpu_index):
             g.replay()
             torch.cuda.synchronize()
         ts.sort()
+        del g
+        S.release_stream(side)        # the graph is gone: its stream's scratch set can serve another stream
         return ts[0], ts[len(ts) // 2]
 
     def flat(t):

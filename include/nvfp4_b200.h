@@ -61,7 +61,7 @@ typedef struct nvfp4_gemm_config {
     int32_t epilogue;  /* 0 auto, 1 = 16-byte global stores, 2 = TMA store, 3 = TMA store with four staging buffers per warp */
     int32_t grid;      /* 0 auto (one CTA per SM), else number of persistent CTAs */
     int32_t cta_group; /* 0 auto, 1 = one CTA per tile, 2 = CTA pair per 256-row tile */
-    int32_t split_k;   /* 0 auto, 1 = persistent stream-K kernel, 2 or 4 = cluster split-K (reduce in DSMEM) */
+    int32_t split_k;   /* 0 auto, 1 = persistent stream-K kernel, 2, 4 or 8 = cluster split-K (reduce in DSMEM; 8 needs tile_n 256) */
 } nvfp4_gemm_config;
 
 /*
@@ -69,8 +69,54 @@ typedef struct nvfp4_gemm_config {
  * cuda_nvfp4_gemm_tcgen05(A, B, SFA, SFB, SFA_perm, SFB_perm, C) of s_128t.py:542-584.
  * Requires n % 128 == 0, k % 256 == 0 (task.yml:24), 16-byte aligned pointers and row strides.
  * Any m >= 1 is accepted (rows past m are not written).  cfg may be NULL.
+ *
+ * Streams: GEMMs issued on different streams may overlap on the GPU.  The persistent kernels keep
+ * fp32 partial tiles and tile counters in library-owned scratch; there is one set per stream,
+ * taken from a pool of eight per device that is allocated with the first GEMM on that device
+ * (make that call outside any graph capture; no later call allocates, also not on a stream seen
+ * for the first time or inside a capture).  A set stays with its stream until
+ * nvfp4_release_stream().  When all are taken, sets of streams whose work has completed are
+ * reused; sets that were used while their stream was being captured are not (the graph may
+ * replay those launches at any time), so release capture streams whose graphs are gone.  If no
+ * set can be had the call returns NVFP4_ERR_UNSUPPORTED and launches nothing.
  */
 int nvfp4_gemm(const nvfp4_problem* problem, const nvfp4_gemm_config* cfg, void* stream);
+
+/*
+ * What the GEMM does with a finished accumulator besides rounding it to fp16: the step that
+ * follows the matmul in a layer, fused into its epilogue.
+ *   out = act(acc + bias[column])          bias fp16 [n] or NULL, added in fp32
+ * written either as fp16 to problem->c or re-quantised to NVFP4 -- packed e2m1 [l][m][n/2] plus one
+ * e4m3 scale per 16 consecutive columns of a row, in the plain [l][m][n/16] layout and / or the
+ * permuted 128 x 4 atom layout: exactly the a / sfa / sfa_perm operands of a following GEMM whose
+ * K is this GEMM's n (and a quarter of the bytes when the output has to travel between GPUs).
+ * The NVFP4 form quantises the fp16-rounded values with the rule of nvfp4_quantize(), so it
+ * equals that function applied to the fp16 output, bit for bit.  SILU is x / (1 + exp(-x)) with
+ * the GPU's fast exponential (not bit-reproducible on a CPU; the others are exact).
+ * The reference writes fp16 only (sub_cub.py:98-104, s_128t.py:324-359); no counterpart.
+ */
+#define NVFP4_ACT_NONE 0
+#define NVFP4_ACT_RELU 1
+#define NVFP4_ACT_SILU 2
+#define NVFP4_OUT_FP16 0
+#define NVFP4_OUT_NVFP4 1
+typedef struct nvfp4_epilogue {
+    const void* bias;   /* fp16 [n], 16-byte aligned, or NULL */
+    int32_t activation; /* NVFP4_ACT_* */
+    int32_t output;     /* NVFP4_OUT_FP16: problem->c; NVFP4_OUT_NVFP4: the fields below (problem->c may be NULL) */
+    void* out_packed;   /* packed e2m1, 16-byte aligned */
+    void* out_sf;       /* plain scales or NULL */
+    void* out_sf_perm;  /* permuted scales (ceil(m/128) * (n/64) * 512 bytes per batch) or NULL */
+    int64_t out_packed_row_stride, out_packed_batch_stride; /* bytes; row stride a multiple of 16 */
+    int64_t out_sf_row_stride, out_sf_batch_stride;         /* bytes; row stride even */
+    int64_t out_sf_perm_batch_stride;                       /* bytes */
+} nvfp4_epilogue;
+
+/*
+ * nvfp4_gemm() with the extended epilogue above (same shapes, checks and stream rules; cfg may be
+ * NULL; cluster split-K is limited to split_k 2, the TMA-store epilogues are not used).
+ */
+int nvfp4_gemm_epilogue(const nvfp4_problem* problem, const nvfp4_gemm_config* cfg, const nvfp4_epilogue* epilogue, void* stream);
 
 /*
  * CUDA-core GEMV for n == 1.  Replaces cuda_nvfp4_gemv(A, B, C, SFA, SFB) of
@@ -196,13 +242,24 @@ int nvfp4_quantize(const void* x, int32_t x_is_bf16, void* packed, void* sf_plai
  * share the one array, which keeps the last call's contents: each call re-zeroes the tile
  * counters on `stream` before its kernel, and two calls whose kernels overlap on the GPU
  * (different streams, no dependency) race on the slots -- serialise them.  A bounded wait that
- * runs out inside this variant is recorded in device memory only (the kernel still returns).
+ * runs out inside this variant is recorded in a device word of the same image; nvfp4_check_status()
+ * reads it (and returns NVFP4_ERR_DEVICE_TIMEOUT) without allocating.
  */
 int nvfp4_gemm_static_scratch(const nvfp4_problem* problem, int workers, void* stream);
 
 /*
+ * Gives back the scratch set nvfp4_gemm() assigned to `stream` on the current device (see there).
+ * Call it when no GEMM of that stream is in flight any more and no graph captured on it will be
+ * replayed again, e.g. before destroying the stream.
+ * No counterpart in the reference (one stream, no scratch).
+ */
+int nvfp4_release_stream(void* stream);
+
+/*
  * Waits for `stream` and returns NVFP4_ERR_DEVICE_TIMEOUT if any kernel launched by this
- * library on the current device reported a timed-out wait since the last check, else NVFP4_OK.
+ * library on the current device reported a timed-out wait since the last check, else NVFP4_OK
+ * (kernels of nvfp4_gemm_static_scratch included: their status word lives in device memory and is
+ * copied into a stack variable here, nothing is allocated).
  * The reference has no counterpart (its waits are unbounded spins, s_128t.py:124-183,309-319).
  */
 int nvfp4_check_status(void* stream);

@@ -21,8 +21,12 @@ EXPORTED_SYMBOLS = (
     "nvfp4_selftest_bounded_wait", "nvfp4_scratch_bytes", "nvfp4_launch_count", "nvfp4_last_kernel",
     "nvfp4_shutdown", "nvfp4_last_error", "nvfp4_version", "nvfp4_plan_units", "nvfp4_gemm_static_scratch",
     "nvfp4_interleave_column_blocks", "nvfp4_permute_scales", "nvfp4_gemm_allgather", "nvfp4_quantize", "nvfp4_copy_2d", "nvfp4_copy_column_blocks",
-    "nvfp4_unpermute_scales", "nvfp4_compare_scale_layouts", "nvfp4_gemv_config",
+    "nvfp4_unpermute_scales", "nvfp4_compare_scale_layouts", "nvfp4_gemv_config", "nvfp4_release_stream",
+    "nvfp4_gemm_epilogue",
 )
+
+ACT_NONE, ACT_RELU, ACT_SILU = 0, 1, 2
+OUT_FP16, OUT_NVFP4 = 0, 1
 
 
 class Nvfp4Error(RuntimeError):
@@ -52,6 +56,17 @@ class GemmConfig(ctypes.Structure):
                 ("split_k", c_int32)]
 
 
+class Epilogue(ctypes.Structure):
+    """Mirror of ``struct nvfp4_epilogue``."""
+    _fields_ = [
+        ("bias", c_void_p), ("activation", c_int32), ("output", c_int32),
+        ("out_packed", c_void_p), ("out_sf", c_void_p), ("out_sf_perm", c_void_p),
+        ("out_packed_row_stride", c_int64), ("out_packed_batch_stride", c_int64),
+        ("out_sf_row_stride", c_int64), ("out_sf_batch_stride", c_int64),
+        ("out_sf_perm_batch_stride", c_int64),
+    ]
+
+
 _lib = None
 
 
@@ -66,6 +81,8 @@ def load() -> ctypes.CDLL:
     lib = ctypes.CDLL(str(LIB_PATH))
     lib.nvfp4_gemm.argtypes = [ctypes.POINTER(Problem), ctypes.POINTER(GemmConfig), c_void_p]
     lib.nvfp4_gemm.restype = c_int
+    lib.nvfp4_gemm_epilogue.argtypes = [ctypes.POINTER(Problem), ctypes.POINTER(GemmConfig), ctypes.POINTER(Epilogue), c_void_p]
+    lib.nvfp4_gemm_epilogue.restype = c_int
     lib.nvfp4_gemm_static_scratch.argtypes = [ctypes.POINTER(Problem), c_int, c_void_p]
     lib.nvfp4_gemm_static_scratch.restype = c_int
     lib.nvfp4_interleave_column_blocks.argtypes = [c_void_p, c_void_p, c_int64, c_int32, c_int32, c_int64, c_void_p]
@@ -91,6 +108,8 @@ def load() -> ctypes.CDLL:
     lib.nvfp4_gemv_config.restype = c_int
     lib.nvfp4_matmul.argtypes = [ctypes.POINTER(Problem), c_void_p]
     lib.nvfp4_matmul.restype = c_int
+    lib.nvfp4_release_stream.argtypes = [c_void_p]
+    lib.nvfp4_release_stream.restype = c_int
     lib.nvfp4_check_status.argtypes = [c_void_p]
     lib.nvfp4_check_status.restype = c_int
     lib.nvfp4_set_wait_timeout_ns.argtypes = [c_uint64]

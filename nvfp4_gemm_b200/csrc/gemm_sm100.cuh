@@ -28,6 +28,7 @@
 // Replaces the reference's single-stage, fully serialised kernel (s_128t.py:375-466).
 #pragma once
 #include "ptx.cuh"
+#include "quantize.cuh"
 
 namespace nvfp4 {
 
@@ -38,8 +39,16 @@ constexpr int kMmaPerStage = 4;    // K = 64 per tcgen05.mma
 constexpr int kSfAtomBytes = 512;  // 128 rows x 4 scales
 constexpr int kGemmThreads = 192;
 constexpr int kTmemCols = 512;
-constexpr int kSfaCol = 256;       // TMEM column of SFA buffer 0 (16 columns per buffer)
-constexpr int kSfbCol = 320;       // TMEM column of SFB buffer 0 (BN/8 columns per buffer)
+// TMEM columns.  128-wide tiles: two accumulators [0,128) and [128,256), scale buffers behind
+// them.  256-wide tiles of the persistent kernels: two accumulators that OVERLAP by half,
+// X = [0,256) and Y = [128,384), scale buffers at [384,480).  The epilogue drains the shared
+// half [128,256) first and hands the accumulator back as soon as it is in registers, so the next
+// tile's MMAs (into the other accumulator) run while the rest is drained and stored; two full
+// 256-column accumulators plus the scale columns would not fit the 512 columns of an SM.
+constexpr int kSfaColPlain = 256, kSfbColPlain = 320;      // SFA / SFB buffer 0 (16 and BN/8 columns per buffer)
+constexpr int kSfaColOverlap = 384, kSfbColOverlap = 416;
+
+enum Activation : int { kActNone = 0, kActRelu = 1, kActSilu = 2 };
 
 enum GemmStatus : int {
     kStatusOk = 0,
@@ -58,6 +67,18 @@ struct GemmParams {
     // stores only; nothing is ever loaded from a peer).
     __half* c_peer[7];
     int n_peer;
+    // Extended epilogue (kernels instantiated with EPI_EX): out = act(acc + bias[column]), written
+    // as fp16 to c, or re-quantised to NVFP4 (packed e2m1 + one e4m3 scale per 16 columns of a row,
+    // the operand format of a following GEMM whose K is this GEMM's N).
+    const __half* bias;          // [N] or null
+    int activation;              // kActNone / kActRelu / kActSilu
+    int out_nvfp4;               // 0: fp16 to c; 1: packed + scales
+    uint8_t* out_packed;         // [L][M][N/2]
+    uint8_t* out_sf;             // plain [L][M][N/16] or null
+    uint8_t* out_sf_perm;        // 512-byte atoms (128 rows x 4 scales), [L][ceil(M/128)][N/64][512], or null
+    long long out_packed_row_stride, out_packed_batch_stride;   // bytes
+    long long out_sf_row_stride, out_sf_batch_stride;           // bytes
+    long long out_sf_perm_batch_stride;                         // bytes
     float* scratch;      // partial-tile slots [worker][head|tail][cta of pair][BN/4][128][4] fp32
     int* counters;       // [worker][cta of pair] k-tiles published per shared tile; zero between launches
     int* status;         // host-visible status word
@@ -92,7 +113,9 @@ struct GemmSmem {
     static constexpr uint32_t kFixBufs = 12;  // barriers reserved for the landing slots
     static constexpr uint32_t kEpiOff = STAGES * kStageBytes;
     static constexpr uint32_t kBarOff = kEpiOff + kEpiBytes;
-    static constexpr uint32_t kNumAcc = (BN <= 128) ? 2 : 1;
+    static constexpr bool kAccOverlap = (BN == 256 && KS == 1);        // see the TMEM column map above
+    static constexpr uint32_t kNumAcc = (BN <= 128 || kAccOverlap) ? 2 : 1;
+    static constexpr uint32_t kAccStride = kAccOverlap ? BN / 2 : BN;  // TMEM columns between the two accumulators
     // full[STAGES] empty[STAGES] acc_full[2] acc_empty[2] fix_full[kFixBufs] | tmem slot | abort | finisher
     static constexpr uint32_t kNumBars = 2 * STAGES + 4 + kFixBufs;
     static constexpr uint32_t kBytes = kBarOff + kNumBars * 8 + 16;
@@ -139,10 +162,18 @@ __device__ __forceinline__ uint4 pack8_fp16(const uint32_t* v) {
     return pack8_fp16(f);
 }
 
-template <int CG, int BN, int STAGES, bool TMA_STORE, int EPI_KB, int KS = 1>
+template <int CG, int BN, int STAGES, bool TMA_STORE, int EPI_KB, int KS = 1, bool EPI_EX = false>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __grid_constant__ GemmParams p) {
+    static_assert(!(EPI_EX && TMA_STORE), "the extended epilogue writes with plain stores");
     using S = GemmSmem<CG, BN, STAGES, TMA_STORE, EPI_KB, KS>;
     constexpr int kNumAcc = S::kNumAcc;
+    constexpr bool kAccOverlap = S::kAccOverlap;
+    constexpr int kSfaCol = kAccOverlap ? kSfaColOverlap : kSfaColPlain;
+    constexpr int kSfbCol = kAccOverlap ? kSfbColOverlap : kSfbColPlain;
+    constexpr int kChunks = BN / 32;                                   // 32-column pieces of an accumulator row
+    // An overlapped accumulator is drained shared half first and released once that half is in
+    // registers; a plain one after its last column.
+    constexpr int kReleaseAfter = kAccOverlap ? kChunks / 2 : kChunks;
     constexpr int kSfbColsPerMma = BN / 32;  // 4 TMEM columns per 128 rows of B
     constexpr int kBRows = S::kBRows;
 
@@ -250,6 +281,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
         const uint64_t pol_b = (p.tiles_m * CG <= 2) ? ptx::policy_evict_first() : ptx::policy_evict_last();
         uint32_t stage = 0, phase = 0;
         bool ok = true;
+#ifdef NVFP4_TRACE
+        int trace_prod_it = 0;
+#endif
         for (int u = u_begin; u < u_end && ok;) {
             const int tile = u / KT;
             const int k0 = u - tile * KT;
@@ -265,6 +299,33 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                     NVFP4_TRACE_END(trace_wait);
                 }
                 if (!ok) break;
+#ifdef NVFP4_TRACE
+                const bool trace_fake = (p.dbg_flags & 8) && trace_prod_it >= STAGES;   // no loads after the first lap
+                const bool trace_no_b = (p.dbg_flags & 16) != 0;
+                ++trace_prod_it;
+                if (trace_fake) {
+                    if (ptx::elect_one() && (CG == 1 || leader)) ptx::mbar_arrive(bar_full + stage * 8);
+                } else if (trace_no_b) {
+                    if (ptx::elect_one()) {
+                        const uint32_t sa = smem_base + stage * S::kStageBytes;
+                        const uint32_t ssfa = sa + S::kABytes + S::kBBytes;
+                        const uint32_t ssfb = ssfa + S::kSfaBytes;
+                        if constexpr (CG == 1) {
+                            const uint32_t full = bar_full + stage * 8;
+                            ptx::mbar_expect_tx(full, S::kStageBytes - S::kBBytes);
+                            ptx::tma_load_3d(sa, &p.tma_a, kt * kBKBytes, mb * kBM, l, full, pol_a);
+                            ptx::tma_load_4d(ssfa, &p.tma_sfa, 0, kt * kMmaPerStage, mb, l, full);
+                            ptx::tma_load_4d(ssfb, &p.tma_sfb, 0, kt * kMmaPerStage, nb * (BN / 128), l, full);
+                        } else {
+                            const uint32_t full = ptx::mapa_u32(bar_full + stage * 8, 0);
+                            if (leader) ptx::mbar_expect_tx(bar_full + stage * 8, 2 * (S::kStageBytes - S::kBBytes));
+                            ptx::tma_load_3d_pair(sa, &p.tma_a, kt * kBKBytes, mb * kBM, l, full, pol_a);
+                            ptx::tma_load_4d_pair(ssfa, &p.tma_sfa, 0, kt * kMmaPerStage, mb, l, full);
+                            ptx::tma_load_4d_pair(ssfb, &p.tma_sfb, 0, kt * kMmaPerStage, nb * (BN / 128), l, full);
+                        }
+                    }
+                } else
+#endif
                 if (ptx::elect_one()) {
                     const uint32_t sa = smem_base + stage * S::kStageBytes;
                     const uint32_t sb = sa + S::kABytes;
@@ -308,16 +369,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                 const int k0 = u - tile * KT;
                 const int k1 = min(KT, k0 + (u_end - u));
                 const uint32_t acc = acc_it % kNumAcc;
-                const uint32_t acc_phase = (acc_it / kNumAcc) & 1u;
+                // Overlapped accumulators: one hand-back per tile on barrier 0 (the previous tile's
+                // shared half is drained; the tile before that, in this accumulator, was drained
+                // earlier by the same threads).  Plain: one barrier per accumulator.
+                const uint32_t empty_bar = bar_acc_empty + (kAccOverlap ? 0u : acc * 8);
+                const uint32_t empty_phase = kAccOverlap ? (acc_it & 1u) : ((acc_it / kNumAcc) & 1u);
                 {
                     NVFP4_TRACE_BEGIN();
-                    ok = ptx::mbar_wait_bounded(bar_acc_empty + acc * 8, acc_phase ^ 1u, abort_flag, timeout);
+                    ok = ptx::mbar_wait_bounded(empty_bar, empty_phase ^ 1u, abort_flag, timeout);
                     ok = __all_sync(0xffffffffu, ok);
                     NVFP4_TRACE_END(trace_wait2);
                 }
                 if (!ok) break;
                 ptx::tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * BN;
+                const uint32_t d_tmem = tmem_base + acc * S::kAccStride;
                 for (int kt = k0; kt < k1; ++kt) {
                     {
                         NVFP4_TRACE_BEGIN();
@@ -425,7 +490,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
             if (!ptx::named_bar_and(2, 128, got_acc)) break;
             NVFP4_TRACE_BEGIN();
             ptx::tc_fence_after();
-            const uint32_t t_acc = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
+            const uint32_t t_acc = tmem_base + acc * S::kAccStride + (static_cast<uint32_t>(quad * 32) << 16);
+            // drain order: position p reads chunk (p + first_chunk) mod kChunks, so that the half an
+            // overlapped accumulator shares with the other one comes first
+            const int first_chunk = (kAccOverlap && acc == 0) ? kChunks / 2 : 0;
+            auto chunk_at = [&](int pos) { return (pos + first_chunk) & (kChunks - 1); };
             const bool whole_tile = (k1 - k0 == KT);
             const int row = mb * kBM + row_in_tile;
             const long long c_off = l * p.c_batch_stride + static_cast<long long>(row) * p.c_row_stride + nb * BN;
@@ -433,10 +502,70 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                 *reinterpret_cast<uint4*>(p.c + c_off + col) = q;
                 for (int r = 0; r < p.n_peer; ++r) *reinterpret_cast<uint4*>(p.c_peer[r] + c_off + col) = q;
             };
+            // 32 finished columns [c0, c0 + 32) of this thread's row, fp32: the plain kernels round to
+            // fp16 and store; the extended epilogue adds the bias, applies the activation and writes
+            // fp16 or NVFP4.  The NVFP4 form quantises the fp16-ROUNDED values, so the result equals
+            // the stand-alone quantiser run on the fp16 output.
+            auto emit32 = [&](int c0, float (&s)[32]) {
+                if constexpr (!EPI_EX) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) store8(c0 + 8 * j, pack8_fp16(&s[8 * j]));
+                } else {
+                    const int gcol = nb * BN + c0;
+                    if (p.bias != nullptr) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint4 b8 = *reinterpret_cast<const uint4*>(p.bias + gcol + 8 * j);
+                            const uint32_t w[4] = {b8.x, b8.y, b8.z, b8.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+                                s[8 * j + 2 * e] = __fadd_rn(s[8 * j + 2 * e], f.x);
+                                s[8 * j + 2 * e + 1] = __fadd_rn(s[8 * j + 2 * e + 1], f.y);
+                            }
+                        }
+                    }
+                    if (p.activation == kActRelu) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) s[i] = fmaxf(s[i], 0.f);
+                    } else if (p.activation == kActSilu) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) s[i] = __fdividef(s[i], 1.f + __expf(-s[i]));
+                    }
+                    if (!p.out_nvfp4) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) store8(c0 + 8 * j, pack8_fp16(&s[8 * j]));
+                    } else {
+                        uint32_t q[4];
+                        uint8_t sf[2];
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            float v[16];
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) v[i] = __half2float(__float2half_rn(s[16 * h + i]));
+                            uint32_t o[2];
+                            sf[h] = quantize_block16(v, o);
+                            q[2 * h] = o[0];
+                            q[2 * h + 1] = o[1];
+                        }
+                        *reinterpret_cast<uint4*>(p.out_packed + l * p.out_packed_batch_stride + static_cast<long long>(row) * p.out_packed_row_stride +
+                                                  gcol / 2) = make_uint4(q[0], q[1], q[2], q[3]);
+                        const uint16_t sf2 = static_cast<uint16_t>(sf[0] | (sf[1] << 8));
+                        const int blk = gcol / 16;      // even: the two scales are neighbours in both layouts
+                        if (p.out_sf != nullptr)
+                            *reinterpret_cast<uint16_t*>(p.out_sf + l * p.out_sf_batch_stride + static_cast<long long>(row) * p.out_sf_row_stride + blk) = sf2;
+                        if (p.out_sf_perm != nullptr)
+                            *reinterpret_cast<uint16_t*>(p.out_sf_perm + l * p.out_sf_perm_batch_stride +
+                                                         (static_cast<long long>(row / 128) * (p.N / 64) + blk / 4) * 512 + (row % 32) * 16 +
+                                                         ((row / 32) % 4) * 4 + (blk % 4)) = sf2;
+                    }
+                }
+            };
             auto release_acc = [&]() {
                 ptx::tc_fence_before();
-                if (CG == 2 && !leader) ptx::mbar_arrive_cluster(bar_acc_empty + acc * 8, 0);
-                else ptx::mbar_arrive(bar_acc_empty + acc * 8);
+                const uint32_t bar = bar_acc_empty + (kAccOverlap ? 0u : acc * 8);
+                if (CG == 2 && !leader) ptx::mbar_arrive_cluster(bar, 0);
+                else ptx::mbar_arrive(bar);
             };
 
             if constexpr (KS > 1) {
@@ -497,11 +626,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                             }
                         }
                     }
-                    if (row < p.M) {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            store8(ks_rank * kMyCols + c0 + 8 * j, pack8_fp16(&s[8 * j]));
-                    }
+                    if (row < p.M) emit32(ks_rank * kMyCols + c0, s);
                 }
                 release_acc();
             } else if (whole_tile) {
@@ -515,19 +640,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                     // as soon as the last column is in registers, before anything is stored: the TMA
                     // stores queue behind the producer's loads in the same TMA unit and are slow to
                     // free their staging buffer.
-                    constexpr int kLoads = BN / 32;
-                    uint32_t packed[BN / 2];
+                    uint32_t packed[BN / 2];          // by drain position
                     uint32_t v[2][32];
-                    ptx::tc_ld_32cols(t_acc, v[0]);
+                    ptx::tc_ld_32cols(t_acc + chunk_at(0) * 32, v[0]);
 #pragma unroll
-                    for (int ci = 0; ci < kLoads; ++ci) {
+                    for (int pos = 0; pos < kChunks; ++pos) {
                         ptx::tc_wait_ld();
-                        if (ci + 1 < kLoads) ptx::tc_ld_32cols(t_acc + (ci + 1) * 32, v[(ci + 1) & 1]);
-                        else release_acc();
+                        if (pos + 1 < kChunks) ptx::tc_ld_32cols(t_acc + chunk_at(pos + 1) * 32, v[(pos + 1) & 1]);
+                        if (pos + 1 == kReleaseAfter) release_acc();
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
-                            const __half2 h = __floats2half2_rn(__uint_as_float(v[ci & 1][2 * j]), __uint_as_float(v[ci & 1][2 * j + 1]));
-                            packed[ci * 16 + j] = *reinterpret_cast<const uint32_t*>(&h);
+                            const __half2 h = __floats2half2_rn(__uint_as_float(v[pos & 1][2 * j]), __uint_as_float(v[pos & 1][2 * j + 1]));
+                            packed[pos * 16 + j] = *reinterpret_cast<const uint32_t*>(&h);
                         }
                     }
                     // Phase 2, store: 64 columns (128 bytes of fp16) at a time through the swizzled
@@ -545,7 +669,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                         ptx::fence_proxy_async_smem();
                         __syncwarp();
                         if (lane == 0 && mb * kBM + quad * 32 < p.M) {  // rows past M inside the box are clipped; one fixed lane owns the bulk groups
-                            ptx::tma_store_3d(&p.tma_c, staging + store_buf * 4096, nb * BN + ci * 64, mb * kBM + quad * 32, l);
+                            ptx::tma_store_3d(&p.tma_c, staging + store_buf * 4096, nb * BN + chunk_at(2 * ci) * 32, mb * kBM + quad * 32, l);
                             ptx::bulk_commit_group();
                         }
                         if (p.n_peer > 0) {
@@ -563,7 +687,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                             const int row_base = mb * kBM + quad * 32;
                             for (int pi = 0; pi < p.n_peer; ++pi) {
                                 const int r = (pi + static_cast<int>(blockIdx.x)) % p.n_peer;   // spread the start over CTAs
-                                __half* dst = p.c_peer[r] + l * p.c_batch_stride + nb * BN + ci * 64 + piece * 8;
+                                __half* dst = p.c_peer[r] + l * p.c_batch_stride + nb * BN + chunk_at(2 * ci) * 32 + piece * 8;
 #pragma unroll
                                 for (int it = 0; it < 8; ++it) {
                                     const int grow = row_base + it * 4 + sub;
@@ -575,16 +699,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                     }
                 } else {
 #pragma unroll 1
-                    for (int c0 = 0; c0 < BN; c0 += 32) {
+                    for (int pos = 0; pos < kChunks; ++pos) {
+                        const int c0 = chunk_at(pos) * 32;
                         uint32_t v[32];
                         ptx::tc_ld_32cols(t_acc + c0, v);
                         ptx::tc_wait_ld();
+                        if (pos + 1 == kReleaseAfter) release_acc();
                         if (row < p.M) {
+                            float s[32];
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) store8(c0 + 8 * j, pack8_fp16(&v[8 * j]));
+                            for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(v[i]);
+                            emit32(c0, s);
                         }
                     }
-                    release_acc();
                 }
             } else {
                 // Tile shared with other workers.  Whoever holds the START of the tile's k-range
@@ -603,17 +730,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                     // contiguous (512 bytes) and a 32-column chunk contiguous (16 KB).
                     float* my_slot = p.scratch + static_cast<long long>(partial_slot(worker, k0, CG, cta_rank)) * (kBM * BN);
 #pragma unroll 1
-                    for (int c0 = 0; c0 < BN; c0 += 32) {
+                    for (int pos = 0; pos < kChunks; ++pos) {
+                        const int c0 = chunk_at(pos) * 32;
                         uint32_t v[32];
                         ptx::tc_ld_32cols(t_acc + c0, v);
                         ptx::tc_wait_ld();
+                        if (pos + 1 == kReleaseAfter) release_acc();  // the MMA warp may start the next tile now
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
                             ptx::st_cg_v4(my_slot + ((c0 / 4 + j) * kBM + row_in_tile) * 4,
                                           make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
                                                       __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
                     }
-                    release_acc();  // the MMA warp may start the next tile now
                     __threadfence();
                     ptx::named_bar_sync(1, 128);
                     if (epi_tid == 0) atomicAdd(counter, k1 - k0);
@@ -684,10 +812,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                                 if (epi_tid == 0) issue(q + kSlots);
                             }
                         }
-                        if (row < p.M && fix_ok) {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) store8(ci * 32 + 8 * j, pack8_fp16(&s[8 * j]));
-                        }
+                        if (row < p.M && fix_ok) emit32(ci * 32, s);
                     }
                     release_acc();
                     if (epi_tid == 0) *counter = 0;

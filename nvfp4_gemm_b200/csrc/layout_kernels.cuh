@@ -10,6 +10,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "quantize.cuh"
+
 namespace nvfp4 {
 
 // One thread moves 16 bytes (8 fp16).  n_local is a multiple of 8.
@@ -183,27 +185,8 @@ __global__ void __launch_bounds__(256) quantize_nvfp4_kernel(const void* __restr
                 v[2 * j + 1] = f.y;
             }
         }
-        float amax = 0.f;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
-        // scale byte: round-to-nearest-even, saturating e4m3 of amax / 6
-        uint16_t sf_pair;
-        const float want = __fdiv_rn(amax, 6.0f);
-        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(sf_pair) : "f"(0.0f), "f"(want));
-        const uint8_t sf_byte = static_cast<uint8_t>(sf_pair & 0xff);
-        uint32_t sf_h2;
-        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(sf_h2) : "h"(sf_pair));
-        const float scale = __low2float(*reinterpret_cast<__half2*>(&sf_h2));
-        uint32_t out[2] = {0u, 0u};
-        if (scale > 0.f) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float a = __fdiv_rn(v[2 * j], scale), b = __fdiv_rn(v[2 * j + 1], scale);
-                uint32_t byte;
-                asm("{\n\t.reg .b8 q;\n\tcvt.rn.satfinite.e2m1x2.f32 q, %1, %2;\n\tcvt.u32.u8 %0, q;\n\t}" : "=r"(byte) : "f"(b), "f"(a));
-                out[j >> 2] |= byte << (8 * (j & 3));
-            }
-        }
+        uint32_t out[2];
+        const uint8_t sf_byte = quantize_block16(v, out);
         *reinterpret_cast<uint2*>(packed + row * packed_row_stride + blk * 8) = make_uint2(out[0], out[1]);
         if (sf_plain) sf_plain[row * sf_plain_row_stride + blk] = sf_byte;
         if (sf_perm) {

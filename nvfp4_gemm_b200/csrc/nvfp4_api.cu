@@ -63,13 +63,23 @@ struct MapEntry {
 constexpr int kMaxCtas = 160;                                          // persistent CTAs (one per SM; a B200 has 148)
 constexpr size_t kSlotBytes = static_cast<size_t>(kBM) * 256 * sizeof(float);  // one 128 x 256 fp32 partial tile
 constexpr size_t kScratchBytes = kMaxCtas * 2 * kSlotBytes;             // head + tail slot per CTA
+// GEMMs on different streams may overlap on the GPU, so the partial-tile scratch and the tile
+// counters are per stream: a fixed number of sets is allocated with the first GEMM on a device
+// and handed to streams as they show up (no allocation then, so a stream may first be seen
+// inside a graph capture).  A set stays with its stream until nvfp4_release_stream(); when all
+// are taken, sets of streams that have gone idle are taken back -- except sets that were used
+// while their stream was being captured: a graph may replay those launches at any later time.
+constexpr int kStreamSets = 8;
 
 struct DeviceCtx {
     int device = -1;
     int num_sms = 0;
     bool sm100 = false;
-    float* scratch = nullptr;
-    int* counters = nullptr;
+    float* scratch = nullptr;    // kStreamSets sets of partial-tile slots
+    int* counters = nullptr;     // kStreamSets sets of tile counters
+    cudaStream_t set_stream[kStreamSets] = {};
+    bool set_used[kStreamSets] = {};
+    bool set_in_graph[kStreamSets] = {};   // a launch with this set was recorded into a CUDA graph
     int* status_host = nullptr;
     int* status_dev = nullptr;
     size_t scratch_bytes = 0;
@@ -78,7 +88,7 @@ struct DeviceCtx {
 #endif
     int max_pairs = -1;  // CTA pairs that can be co-resident (cluster occupancy), queried once
     std::vector<MapEntry> maps;
-    bool smem_attr_set[16] = {};
+    bool smem_attr_set[24] = {};
 };
 
 std::mutex g_mutex;
@@ -119,16 +129,53 @@ int ensure_scratch(DeviceCtx* c) {
     if (c->scratch) return NVFP4_OK;
     // Partial-tile slots need no initialisation (they are written before they are read); the
     // per-tile counters must be zero between launches.
-    CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&c->scratch), kScratchBytes));
-    CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&c->counters), kMaxCtas * sizeof(int)));
-    CUDA_TRY(cudaMemset(c->counters, 0, kMaxCtas * sizeof(int)));
+    CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&c->scratch), kStreamSets * kScratchBytes));
+    CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&c->counters), kStreamSets * kMaxCtas * sizeof(int)));
+    CUDA_TRY(cudaMemset(c->counters, 0, kStreamSets * kMaxCtas * sizeof(int)));
 #ifdef NVFP4_TRACE
     CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&c->trace), kMaxCtas * 16 * sizeof(unsigned long long)));
     CUDA_TRY(cudaMemset(c->trace, 0, kMaxCtas * 16 * sizeof(unsigned long long)));
 #endif
     CUDA_TRY(cudaDeviceSynchronize());
-    c->scratch_bytes = kScratchBytes + kMaxCtas * sizeof(int);
+    c->scratch_bytes = kStreamSets * (kScratchBytes + kMaxCtas * sizeof(int));
     return NVFP4_OK;
+}
+
+// The scratch set of `stream` on this device.
+int scratch_set_for(DeviceCtx* c, cudaStream_t stream, int* set) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    for (int i = 0; i < kStreamSets; ++i)
+        if (c->set_used[i] && c->set_stream[i] == stream) {
+            *set = i;
+            if (!c->set_in_graph[i]) {   // (once set, the flag stays: nothing more to find out)
+                cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+                if (cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone) c->set_in_graph[i] = true;
+            }
+            return NVFP4_OK;
+        }
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    CUDA_TRY(cudaStreamIsCapturing(stream, &cap));
+    const bool capturing = (cap != cudaStreamCaptureStatusNone);
+    for (int pass = 0; pass < 2; ++pass) {
+        for (int i = 0; i < kStreamSets; ++i)
+            if (!c->set_used[i]) {
+                c->set_used[i] = true;
+                c->set_stream[i] = stream;
+                c->set_in_graph[i] = capturing;
+                *set = i;
+                return NVFP4_OK;
+            }
+        // All taken.  Outside a capture (stream queries are not allowed during one), take back the
+        // sets of streams whose work is complete and that no graph refers to.
+        if (capturing || pass == 1) break;
+        for (int i = 0; i < kStreamSets; ++i)
+            if (c->set_used[i] && !c->set_in_graph[i] && cudaStreamQuery(c->set_stream[i]) != cudaErrorNotReady) c->set_used[i] = false;
+        (void)cudaGetLastError();   // a query of a stream that was destroyed meanwhile leaves an error behind
+    }
+    return fail(NVFP4_ERR_UNSUPPORTED,
+                "all %d scratch sets of device %d belong to busy streams or to streams that were captured into graphs: "
+                "call nvfp4_release_stream() for streams (and graphs) that are done",
+                kStreamSets, c->device);
 }
 
 // Tensor maps are cached by (pointer, extents, strides, box): re-encoding four maps per call,
@@ -197,10 +244,10 @@ MapKey make_sf_key(const void* ptr, int rows, int k, int l, uint64_t batch_strid
 
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
-template <int CG, int BN, int STAGES, bool TMA_STORE, int EPI_KB>
+template <int CG, int BN, int STAGES, bool TMA_STORE, int EPI_KB, bool EPI_EX = false>
 int launch_gemm(DeviceCtx* c, int variant, GemmParams& params, int grid_request, cudaStream_t stream, const char* name) {
     using S = GemmSmem<CG, BN, STAGES, TMA_STORE, EPI_KB>;
-    auto kernel = gemm_nvfp4_kernel<CG, BN, STAGES, TMA_STORE, EPI_KB>;
+    auto kernel = gemm_nvfp4_kernel<CG, BN, STAGES, TMA_STORE, EPI_KB, 1, EPI_EX>;
     if (!c->smem_attr_set[variant]) {
         CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamicBytes));
         c->smem_attr_set[variant] = true;
@@ -260,10 +307,10 @@ int launch_gemm(DeviceCtx* c, int variant, GemmParams& params, int grid_request,
 }
 
 // Cluster split-K launch: one cluster of KS CTAs per 128 x BN output tile.
-template <int BN, int STAGES, int EPI_KB, int KS>
+template <int BN, int STAGES, int EPI_KB, int KS, bool EPI_EX = false>
 int launch_gemm_splitk(DeviceCtx* c, int variant, GemmParams& params, cudaStream_t stream, const char* name) {
     using S = GemmSmem<1, BN, STAGES, false, EPI_KB, KS>;
-    auto kernel = gemm_nvfp4_kernel<1, BN, STAGES, false, EPI_KB, KS>;
+    auto kernel = gemm_nvfp4_kernel<1, BN, STAGES, false, EPI_KB, KS, EPI_EX>;
     if (!c->smem_attr_set[variant]) {
         CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kDynamicBytes));
         c->smem_attr_set[variant] = true;
@@ -312,21 +359,21 @@ int validate_common(const nvfp4_problem* p) {
     if (!p) return fail(NVFP4_ERR_INVALID_ARGUMENT, "problem is NULL");
     if (p->m < 1 || p->n < 1 || p->k < 1 || p->l < 1)
         return fail(NVFP4_ERR_INVALID_ARGUMENT, "m, n, k, l must be positive (got %d, %d, %d, %d)", p->m, p->n, p->k, p->l);
-    if (!p->a || !p->b || !p->c) return fail(NVFP4_ERR_INVALID_ARGUMENT, "a, b and c must not be NULL");
+    if (!p->a || !p->b) return fail(NVFP4_ERR_INVALID_ARGUMENT, "a and b must not be NULL");
     return NVFP4_OK;
 }
 
-}  // namespace
-
-namespace {
-int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* const* c_peers, int n_peers, void* stream_v) {
+// Everything both GEMM entry points require of a problem, checked before any CUDA call.
+int validate_gemm(const nvfp4_problem* p, bool needs_c = true) {
     if (int rc = validate_common(p)) return rc;
+    if (needs_c && !p->c) return fail(NVFP4_ERR_INVALID_ARGUMENT, "c must not be NULL");
     if (!p->sfa_perm || !p->sfb_perm)
         return fail(NVFP4_ERR_INVALID_ARGUMENT, "the GEMM needs the permuted scale tensors (sfa_perm, sfb_perm)");
     if (p->k % kKPerStage) return fail(NVFP4_ERR_INVALID_ARGUMENT, "k must be a multiple of 256 (got %d)", p->k);
     if (p->n % 128) return fail(NVFP4_ERR_INVALID_ARGUMENT, "n must be a multiple of 128 (got %d)", p->n);
     if (!aligned(p->a, 16) || !aligned(p->b, 16) || !aligned(p->c, 16) || !aligned(p->sfa_perm, 16) || !aligned(p->sfb_perm, 16))
         return fail(NVFP4_ERR_INVALID_ARGUMENT, "a, b, c, sfa_perm and sfb_perm must be 16-byte aligned");
+    if (!needs_c && !p->c) return NVFP4_OK;     // no fp16 output: its strides mean nothing
     if (p->a_row_stride % 16 || p->b_row_stride % 16 || p->a_row_stride < p->k / 2 || p->b_row_stride < p->k / 2)
         return fail(NVFP4_ERR_INVALID_ARGUMENT, "row strides of a and b must be multiples of 16 bytes and >= k/2");
     if (p->c_row_stride % 8 || p->c_row_stride < p->n)
@@ -334,6 +381,38 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* const*
     if (p->l > 1 && (p->a_batch_stride % 16 || p->b_batch_stride % 16 || p->c_batch_stride % 8 ||
                      p->sfa_perm_batch_stride % 16 || p->sfb_perm_batch_stride % 16))
         return fail(NVFP4_ERR_INVALID_ARGUMENT, "batch strides must keep 16-byte alignment");
+    return NVFP4_OK;
+}
+
+}  // namespace
+
+namespace {
+int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, const nvfp4_epilogue* epi, void* const* c_peers, int n_peers,
+              void* stream_v) {
+    const bool to_nvfp4 = epi && epi->output == NVFP4_OUT_NVFP4;
+    if (int rc = validate_gemm(p, !to_nvfp4)) return rc;
+    if (epi) {
+        if (epi->activation < NVFP4_ACT_NONE || epi->activation > NVFP4_ACT_SILU)
+            return fail(NVFP4_ERR_INVALID_ARGUMENT, "activation must be NVFP4_ACT_NONE, NVFP4_ACT_RELU or NVFP4_ACT_SILU");
+        if (epi->output != NVFP4_OUT_FP16 && epi->output != NVFP4_OUT_NVFP4)
+            return fail(NVFP4_ERR_INVALID_ARGUMENT, "output must be NVFP4_OUT_FP16 or NVFP4_OUT_NVFP4");
+        if (epi->bias && !aligned(epi->bias, 16)) return fail(NVFP4_ERR_INVALID_ARGUMENT, "bias must be 16-byte aligned");
+        if (n_peers > 0) return fail(NVFP4_ERR_UNSUPPORTED, "the fused all-gather writes fp16 without bias or activation");
+        if (to_nvfp4) {
+            if (!epi->out_packed || (!epi->out_sf && !epi->out_sf_perm))
+                return fail(NVFP4_ERR_INVALID_ARGUMENT, "NVFP4 output needs out_packed and at least one of out_sf / out_sf_perm");
+            if (!aligned(epi->out_packed, 16) || epi->out_packed_row_stride % 16 || epi->out_packed_row_stride < p->n / 2)
+                return fail(NVFP4_ERR_INVALID_ARGUMENT, "out_packed must be 16-byte aligned with a row stride that is a multiple of 16 and >= n/2");
+            if (epi->out_sf && (!aligned(epi->out_sf, 2) || epi->out_sf_row_stride % 2 || epi->out_sf_row_stride < p->n / 16))
+                return fail(NVFP4_ERR_INVALID_ARGUMENT, "out_sf must be 2-byte aligned with an even row stride >= n/16");
+            if (epi->out_sf_perm && !aligned(epi->out_sf_perm, 16))
+                return fail(NVFP4_ERR_INVALID_ARGUMENT, "out_sf_perm must be 16-byte aligned");
+            const long long perm_bytes = static_cast<long long>((p->m + 127) / 128) * (p->n / 64) * 512;
+            if (p->l > 1 && (epi->out_packed_batch_stride % 16 || epi->out_sf_batch_stride % 2 || epi->out_sf_perm_batch_stride % 16 ||
+                             (epi->out_sf_perm && epi->out_sf_perm_batch_stride < perm_bytes)))
+                return fail(NVFP4_ERR_INVALID_ARGUMENT, "output batch strides too small or misaligned");
+        }
+    }
 
     nvfp4_gemm_config cf = {0, 0, 0, 0, 0};
     if (cfg) cf = *cfg;
@@ -373,8 +452,25 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* const*
     if (units > 0x7fffffffLL) return fail(NVFP4_ERR_INVALID_ARGUMENT, "problem too large: %lld work units", units);
     g.total_units = static_cast<int>(units);
     g.c = static_cast<__half*>(p->c);
-    g.scratch = c->scratch;
-    g.counters = c->counters;
+    if (epi) {
+        g.bias = static_cast<const __half*>(epi->bias);
+        g.activation = epi->activation;
+        g.out_nvfp4 = to_nvfp4 ? 1 : 0;
+        if (to_nvfp4) {
+            g.out_packed = static_cast<uint8_t*>(epi->out_packed);
+            g.out_sf = static_cast<uint8_t*>(epi->out_sf);
+            g.out_sf_perm = static_cast<uint8_t*>(epi->out_sf_perm);
+            g.out_packed_row_stride = epi->out_packed_row_stride;
+            g.out_packed_batch_stride = epi->out_packed_batch_stride;
+            g.out_sf_row_stride = epi->out_sf_row_stride;
+            g.out_sf_batch_stride = epi->out_sf_batch_stride;
+            g.out_sf_perm_batch_stride = epi->out_sf_perm_batch_stride;
+        }
+    }
+    int set = 0;
+    if (int rc = scratch_set_for(c, stream, &set)) return rc;
+    g.scratch = c->scratch + static_cast<size_t>(set) * (kScratchBytes / sizeof(float));
+    g.counters = c->counters + set * kMaxCtas;
     g.status = c->status_dev;
     g.c_row_stride = p->c_row_stride;
     g.c_batch_stride = p->c_batch_stride;
@@ -387,6 +483,14 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* const*
     // Whole tiles leave through the TMA-store epilogue unless the caller asks for plain stores.
     int epilogue = cf.epilogue;
     if (epilogue == 0) epilogue = 2;
+    if (epi) epilogue = 1;                     // the extended epilogue writes with plain stores
+    if (epi && to_nvfp4 && g.out_sf_perm && p->m % 128) {
+        // rows of the last 128-row block that do not exist must read as zero scales
+        const long long per_batch = static_cast<long long>((p->m + 127) / 128) * (p->n / 64) * 512;
+        const long long tail = static_cast<long long>(p->n / 64) * 512;
+        for (int l = 0; l < p->l; ++l)
+            CUDA_TRY(cudaMemsetAsync(g.out_sf_perm + l * g.out_sf_perm_batch_stride + per_batch - tail, 0, tail, stream));
+    }
 
     const uint64_t kbytes = static_cast<uint64_t>(p->k) / 2;
     const uint64_t a_bs = p->l > 1 ? static_cast<uint64_t>(p->a_batch_stride) : static_cast<uint64_t>(p->a_row_stride) * p->m;
@@ -400,7 +504,7 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* const*
     if (int rc = get_map(c, make_sf_key(p->sfb_perm, p->n, p->k, p->l, p->sfb_perm_batch_stride, bn / 128), &g.tma_sfb)) return rc;
     g.n_peer = n_peers;
     for (int i = 0; i < n_peers; ++i) g.c_peer[i] = static_cast<__half*>(c_peers[i]);
-    if (epilogue >= 2) {
+    if (epilogue >= 2 && p->c) {
         if (int rc = get_map(c, make_key(p->c, p->n, p->m, p->l, static_cast<uint64_t>(p->c_row_stride) * 2, c_bs, 64, 32,
                                          CU_TENSOR_MAP_DATA_TYPE_FLOAT16),
                              &g.tma_c)) return rc;
@@ -415,7 +519,7 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* const*
         if (p->m <= kBM && cf.cta_group != 2 && cf.tile_n == 0 && cf.grid == 0) {
             // measured: two CTAs per tile beat four whenever both fit in one wave (the exchange
             // grows with the cluster); four only pays when there are very few tiles
-            if (tiles128 * 4 <= c->num_sms / 2 && g.k_tiles >= 16) ks = 4;
+            if (tiles128 * 4 <= c->num_sms / 2 && g.k_tiles >= 16 && !epi) ks = 4;
             else if (tiles128 * 2 <= c->num_sms && g.k_tiles >= 16) ks = 2;   // shorter K: one whole tile per CTA wins
         }
     }
@@ -434,6 +538,10 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* const*
         if (int rc = get_map(c, make_key(p->b, kbytes, p->n, p->l, p->b_row_stride, b_bs, kBKBytes, bn, CU_TENSOR_MAP_DATA_TYPE_UINT8),
                              &g.tma_b)) return rc;
         if (int rc = get_map(c, make_sf_key(p->sfb_perm, p->n, p->k, p->l, p->sfb_perm_batch_stride, bn / 128), &g.tma_sfb)) return rc;
+        if (epi) {
+            if (bn == 128 && ks == 2) return launch_gemm_splitk<128, 6, 0, 2, true>(c, 16, g, stream, "gemm_splitk2_n128_s6_epilogue");
+            return fail(NVFP4_ERR_UNSUPPORTED, "the extended epilogue is built for split_k 1 and 2");
+        }
         if (bn == 128 && ks == 2) return launch_gemm_splitk<128, 6, 0, 2>(c, 8, g, stream, "gemm_splitk2_n128_s6");
         if (bn == 128) return launch_gemm_splitk<128, 6, 0, 4>(c, 9, g, stream, "gemm_splitk4_n128_s6");
         if (ks == 4) return launch_gemm_splitk<256, 4, 0, 4>(c, 10, g, stream, "gemm_splitk4_n256_s4");
@@ -441,6 +549,12 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* const*
     }
 
     const int grid = cf.grid;
+    if (epi) {
+        if (cg == 2 && bn == 256) return launch_gemm<2, 256, 5, false, 32, true>(c, 17, g, grid, stream, "gemm_2cta_n256_s5_epilogue");
+        if (cg == 2) return launch_gemm<2, 128, 6, false, 32, true>(c, 18, g, grid, stream, "gemm_2cta_n128_s6_epilogue");
+        if (bn == 256) return launch_gemm<1, 256, 3, false, 48, true>(c, 19, g, grid, stream, "gemm_1cta_n256_s3_epilogue");
+        return launch_gemm<1, 128, 4, false, 64, true>(c, 20, g, grid, stream, "gemm_1cta_n128_s4_epilogue");
+    }
     if (cg == 2) {
         if (bn == 256 && epilogue == 3) return launch_gemm<2, 256, 4, true, 64>(c, 12, g, grid, stream, "gemm_2cta_n256_s4_tmastore4");
         if (bn == 256 && epilogue == 2) return launch_gemm<2, 256, 5, true, 32>(c, 4, g, grid, stream, "gemm_2cta_n256_s5_tmastore");
@@ -455,10 +569,19 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* const*
 }
 }  // namespace
 
+// Defined with the static-scratch entry point below: reads and clears that path's status word
+// (0 when the path was never used on `dev`).  Allocates nothing.
+static int static_scratch_take_status(int dev, int* status);
+
 extern "C" {
 
 int nvfp4_gemm(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* stream_v) {
-    return gemm_impl(p, cfg, nullptr, 0, stream_v);
+    return gemm_impl(p, cfg, nullptr, nullptr, 0, stream_v);
+}
+
+int nvfp4_gemm_epilogue(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, const nvfp4_epilogue* epi, void* stream_v) {
+    if (!epi) return fail(NVFP4_ERR_INVALID_ARGUMENT, "epilogue is NULL (use nvfp4_gemm for the plain fp16 output)");
+    return gemm_impl(p, cfg, epi, nullptr, 0, stream_v);
 }
 
 int nvfp4_gemm_allgather(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, void* const* c_peers, int n_peers, void* stream_v) {
@@ -471,7 +594,7 @@ int nvfp4_gemm_allgather(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, v
     nvfp4_gemm_config cf = {0, 0, 0, 0, 0};
     if (cfg) cf = *cfg;
     if (cf.split_k == 0) cf.split_k = 1;
-    return gemm_impl(p, &cf, c_peers, n_peers, stream_v);
+    return gemm_impl(p, &cf, nullptr, c_peers, n_peers, stream_v);
 }
 
 int nvfp4_gemv(const nvfp4_problem* p, void* stream_v) { return nvfp4_gemv_config(p, 0, 0, stream_v); }
@@ -482,6 +605,7 @@ int nvfp4_gemv_config(const nvfp4_problem* p, int rows_per_warp, int warps_per_c
         return fail(NVFP4_ERR_INVALID_ARGUMENT, "rows_per_warp must be 0 (auto), 1, 2 or 4");
     if (warps_per_cta != 0 && warps_per_cta != 1 && warps_per_cta != 2 && warps_per_cta != 4)
         return fail(NVFP4_ERR_INVALID_ARGUMENT, "warps_per_cta must be 0 (auto), 1, 2 or 4");
+    if (!p->c) return fail(NVFP4_ERR_INVALID_ARGUMENT, "c must not be NULL");
     if (p->n != 1) return fail(NVFP4_ERR_INVALID_ARGUMENT, "the GEMV needs n == 1 (got %d)", p->n);
     if (!p->sfa || !p->sfb) return fail(NVFP4_ERR_INVALID_ARGUMENT, "the GEMV needs the plain scale tensors (sfa, sfb)");
     if (p->k % 64) return fail(NVFP4_ERR_INVALID_ARGUMENT, "k must be a multiple of 64 (got %d)", p->k);
@@ -705,19 +829,35 @@ int nvfp4_check_status(void* stream_v) {
     DeviceCtx* c = nullptr;
     if (int rc = get_ctx(&c)) return rc;
     CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream_v)));
+    // kernels of nvfp4_gemm_static_scratch report into their own device word (that path must not
+    // allocate, so it has no host-mapped one): fetch it into a stack variable
+    int static_st = 0;
+    if (int rc = static_scratch_take_status(c->device, &static_st)) return rc;
+    if (static_st != kStatusOk)
+        return fail(NVFP4_ERR_DEVICE_TIMEOUT, "a kernel of nvfp4_gemm_static_scratch gave up on a bounded wait (device status %d)", static_st);
     const int st = *reinterpret_cast<volatile int*>(c->status_host);
     if (st == kStatusOk) return NVFP4_OK;
     *reinterpret_cast<volatile int*>(c->status_host) = 0;
     // A kernel that gave up may have left tile counters half-way: restore the all-zero invariant.
     if (c->scratch) {
         CUDA_TRY(cudaDeviceSynchronize());
-        CUDA_TRY(cudaMemset(c->counters, 0, kMaxCtas * sizeof(int)));
+        CUDA_TRY(cudaMemset(c->counters, 0, kStreamSets * kMaxCtas * sizeof(int)));
         CUDA_TRY(cudaDeviceSynchronize());
     }
     return fail(NVFP4_ERR_DEVICE_TIMEOUT, "a kernel gave up on a bounded wait (device status %d)", st);
 }
 
 uint64_t nvfp4_set_wait_timeout_ns(uint64_t ns) { return g_timeout_ns.exchange(ns); }
+
+int nvfp4_release_stream(void* stream_v) {
+    DeviceCtx* c = nullptr;
+    if (int rc = get_ctx(&c)) return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    for (int i = 0; i < kStreamSets; ++i)
+        if (c->set_used[i] && c->set_stream[i] == stream) c->set_used[i] = false;
+    return NVFP4_OK;
+}
 
 int nvfp4_selftest_bounded_wait(void* stream_v) {
     DeviceCtx* c = nullptr;
@@ -852,23 +992,23 @@ int encode_map_inplace(const MapKey& key, CUtensorMap* out) {
 
 }  // namespace
 
+static int static_scratch_take_status(int dev, int* status) {
+    *status = 0;
+    StaticScratch* st = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        if (dev < 0 || dev >= 64 || !g_static[dev].ready) return NVFP4_OK;
+        st = &g_static[dev];
+    }
+    CUDA_TRY(cudaMemcpy(status, st->status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*status != 0) CUDA_TRY(cudaMemset(st->status, 0, sizeof(int)));
+    return NVFP4_OK;
+}
+
 extern "C" {
 
 int nvfp4_gemm_static_scratch(const nvfp4_problem* p, int workers, void* stream_v) {
-    if (int rc = validate_common(p)) return rc;
-    if (!p->sfa_perm || !p->sfb_perm)
-        return fail(NVFP4_ERR_INVALID_ARGUMENT, "the GEMM needs the permuted scale tensors (sfa_perm, sfb_perm)");
-    if (p->k % kKPerStage) return fail(NVFP4_ERR_INVALID_ARGUMENT, "k must be a multiple of 256 (got %d)", p->k);
-    if (p->n % 128) return fail(NVFP4_ERR_INVALID_ARGUMENT, "n must be a multiple of 128 (got %d)", p->n);
-    if (!aligned(p->a, 16) || !aligned(p->b, 16) || !aligned(p->c, 16) || !aligned(p->sfa_perm, 16) || !aligned(p->sfb_perm, 16))
-        return fail(NVFP4_ERR_INVALID_ARGUMENT, "a, b, c, sfa_perm and sfb_perm must be 16-byte aligned");
-    if (p->a_row_stride % 16 || p->b_row_stride % 16 || p->a_row_stride < p->k / 2 || p->b_row_stride < p->k / 2)
-        return fail(NVFP4_ERR_INVALID_ARGUMENT, "row strides of a and b must be multiples of 16 bytes and >= k/2");
-    if (p->c_row_stride % 8 || p->c_row_stride < p->n)
-        return fail(NVFP4_ERR_INVALID_ARGUMENT, "c_row_stride must be a multiple of 8 elements and >= n");
-    if (p->l > 1 && (p->a_batch_stride % 16 || p->b_batch_stride % 16 || p->c_batch_stride % 8 ||
-                     p->sfa_perm_batch_stride % 16 || p->sfb_perm_batch_stride % 16))
-        return fail(NVFP4_ERR_INVALID_ARGUMENT, "batch strides must keep 16-byte alignment");
+    if (int rc = validate_gemm(p)) return rc;
     if (workers < 0 || workers > kStaticMaxWorkers)
         return fail(NVFP4_ERR_INVALID_ARGUMENT,
                     "workers = %d exceeds what the fixed scratch holds: at most %d persistent CTAs (8 MiB of partial-tile slots)",

@@ -145,6 +145,27 @@ class ColumnParallelGemm:
         self.interleave_fn(self.gathered[idx], dst, p1 - p0, self.shard.n_local, self.world, c_full.stride(0))
 
 
+def symmetric_output(m: int, n: int, device, group):
+    """The full fp16 output [m * n] in symmetric memory, mapped into every rank's address space
+    for PLAIN peer loads and stores: the buffer must not be bound to an NVLink multicast object
+    (none of the kernels here use one, and a rank that dies while bound to one disturbs its
+    peers).  Returns (tensor, rendezvous handle); raises if the binding could not be avoided."""
+    import os
+    os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"     # read by torch when the buffer is exchanged
+    import torch.distributed._symmetric_memory as symm_mem
+    c_sym = symm_mem.empty((m * n,), dtype=torch.float16, device=device)
+    handle = symm_mem.rendezvous(c_sym, group)
+    check_no_multicast(handle)
+    return c_sym, handle
+
+
+def check_no_multicast(handle) -> None:
+    if int(getattr(handle, "multicast_ptr", 0) or 0) != 0:
+        raise RuntimeError("the symmetric output buffer is bound to an NVLink multicast object although "
+                           "TORCH_SYMM_MEM_DISABLE_MULTICAST=1 was set: set it in the environment before torch initialises "
+                           "symmetric memory")
+
+
 class FusedAllGatherGemm:
     """Column-parallel GEMM whose epilogue is the all-gather: each rank's kernel stores every
     finished tile of its column block into its own output AND into the same place of every peer's
@@ -157,10 +178,6 @@ class FusedAllGatherGemm:
     def __init__(self, m: int, n: int, k: int, group=None, device=None, config=None):
         import ctypes
         self.config = config
-        import os
-        # plain peer stores only: do not bind the buffer to an NVLink multicast object
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
-        import torch.distributed._symmetric_memory as symm_mem
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
@@ -169,8 +186,7 @@ class FusedAllGatherGemm:
         self.shard = plan_shard(n, self.world, self.rank)
         self.m, self.n, self.k = m, n, k
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
-        self.c_sym = symm_mem.empty((m * n,), dtype=torch.float16, device=self.device)
-        self.handle = symm_mem.rendezvous(self.c_sym, self.group)
+        self.c_sym, self.handle = symmetric_output(m, n, self.device, self.group)
         self.c_full = self.c_sym.view(1, m, n).permute(1, 2, 0)            # [M, N, 1], row-major
         col_off = self.shard.begin * 2                                      # bytes
         peers = [int(self.handle.buffer_ptrs[r]) + col_off for r in range(self.world) if r != self.rank]
@@ -199,17 +215,13 @@ class CopyEngineAllGatherGemm:
     """
 
     def __init__(self, m: int, n: int, k: int, group=None, device=None, panels: int = 4):
-        import os
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
-        import torch.distributed._symmetric_memory as symm_mem
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
         self.shard = plan_shard(n, self.world, self.rank)
         self.m, self.n, self.k = m, n, k
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
-        self.c_sym = symm_mem.empty((m * n,), dtype=torch.float16, device=self.device)
-        self.handle = symm_mem.rendezvous(self.c_sym, self.group)
+        self.c_sym, self.handle = symmetric_output(m, n, self.device, self.group)
         self.c_full = self.c_sym.view(1, m, n).permute(1, 2, 0)
         self.panels = row_panels(m, panels)
         self.peer_bases = [int(self.handle.buffer_ptrs[r]) for r in range(self.world) if r != self.rank]
@@ -273,9 +285,6 @@ class PanelAllGatherGemm:
 
     def __init__(self, m: int, n: int, k: int, group=None, device=None, panels: int = 4, copy_ctas: int = 0, direction: str = "push"):
         import ctypes
-        import os
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
-        import torch.distributed._symmetric_memory as symm_mem
         if direction not in ("push", "pull"):
             raise ValueError("direction must be 'push' or 'pull'")
         self.direction = direction
@@ -287,8 +296,7 @@ class PanelAllGatherGemm:
         self.shard = plan_shard(n, self.world, self.rank)
         self.m, self.n, self.k = m, n, k
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
-        self.c_sym = symm_mem.empty((m * n,), dtype=torch.float16, device=self.device)
-        self.handle = symm_mem.rendezvous(self.c_sym, self.group)
+        self.c_sym, self.handle = symmetric_output(m, n, self.device, self.group)
         self.c_full = self.c_sym.view(1, m, n).permute(1, 2, 0)
         self.panels = row_panels(m, panels)
         self.copy_ctas = copy_ctas

@@ -28,15 +28,15 @@ def make_problem(data: input_t) -> Problem:
     n = b.shape[0]
     if b.shape[1] != k_bytes or b.shape[2] != l:
         raise ValueError(f"a {tuple(a.shape)} and b {tuple(b.shape)} disagree on k or l")
-    if tuple(c.shape) != (m, n, l):
+    if c is not None and tuple(c.shape) != (m, n, l):
         raise ValueError(f"c has shape {tuple(c.shape)}, expected {(m, n, l)}")
-    if a.stride(1) != 1 or b.stride(1) != 1 or c.stride(1) != 1 and n > 1:
+    if a.stride(1) != 1 or b.stride(1) != 1 or (c is not None and c.stride(1) != 1 and n > 1):
         raise ValueError("a, b must be K-major (stride 1 along k) and c row-major")
-    if a.element_size() != 1 or b.element_size() != 1 or c.dtype != torch.float16 or any(
+    if a.element_size() != 1 or b.element_size() != 1 or (c is not None and c.dtype != torch.float16) or any(
             t is not None and t.element_size() != 1 for t in (sfa, sfb, sfa_perm, sfb_perm)):
         raise ValueError("expected packed fp4 (1 byte per 2 values), 1-byte scales and fp16 output")
     p = Problem()
-    p.a, p.b, p.c = a.data_ptr(), b.data_ptr(), c.data_ptr()
+    p.a, p.b, p.c = a.data_ptr(), b.data_ptr(), (c.data_ptr() if c is not None else None)
     p.sfa = sfa.data_ptr() if sfa is not None else None
     p.sfb = sfb.data_ptr() if sfb is not None else None
     p.sfa_perm = sfa_perm.data_ptr() if sfa_perm is not None else None
@@ -51,7 +51,8 @@ def make_problem(data: input_t) -> Problem:
     # permuted scales: [32, 4, rest_rows, 4, rest_k, L]; the batch is the last dimension
     p.sfa_perm_batch_stride = _batch_stride(sfa_perm, 5) if sfa_perm is not None else 0
     p.sfb_perm_batch_stride = _batch_stride(sfb_perm, 5) if sfb_perm is not None else 0
-    p.c_row_stride, p.c_batch_stride = c.stride(0), _batch_stride(c)
+    if c is not None:
+        p.c_row_stride, p.c_batch_stride = c.stride(0), _batch_stride(c)
     return p
 
 
@@ -108,6 +109,54 @@ def gemm(data: input_t, tile_n: int = 0, epilogue: int = 0, grid: int = 0, cta_g
     return data[6]
 
 
+_ACTIVATIONS = {"none": _lib.ACT_NONE, "relu": _lib.ACT_RELU, "silu": _lib.ACT_SILU}
+
+
+def gemm_epilogue(data: input_t, bias=None, activation: str = "none", nvfp4_out: bool = False, tile_n: int = 0, grid: int = 0,
+                  cta_group: int = 0, split_k: int = 0):
+    """The GEMM with the step that follows it fused into its epilogue: ``act(a @ b.T + bias)``.
+
+    ``nvfp4_out=False`` writes fp16 into ``data[6]`` and returns it.  ``nvfp4_out=True`` returns
+    the result re-quantised to NVFP4 as ``(packed, sf, sf_permuted)`` -- [M, N/2, L] packed e2m1,
+    [M, N/16, L] e4m3 scales and the same scales in the permuted atom layout -- i.e. the ``a``,
+    ``sfa`` and ``sfa_permuted`` of a following ``custom_kernel`` call whose K is this N; ``data[6]``
+    may then be None.  The reference writes fp16 only (sub_cub.py:98-104); no counterpart."""
+    from .inputs import FP4_DTYPE, SF_DTYPE
+    lib = _lib.load()
+    a, b = data[0], data[1]
+    _require_cuda(data)
+    m, _, l = a.shape
+    n = b.shape[0]
+    dev = a.device
+    if data[6] is None and not nvfp4_out:
+        raise ValueError("an fp16 output needs data[6]")
+    problem = make_problem(data)
+    epi = _lib.Epilogue()
+    if bias is not None:
+        if bias.dtype != torch.float16 or bias.numel() != n or not bias.is_contiguous():
+            raise ValueError("bias must be a contiguous fp16 vector of length n")
+        epi.bias = bias.data_ptr()
+    epi.activation = _ACTIVATIONS[activation]
+    out = data[6]
+    if nvfp4_out:
+        packed = torch.empty((l, m, n // 2), dtype=torch.uint8, device=dev)
+        sf = torch.empty((l, m, n // 16), dtype=torch.uint8, device=dev)
+        rest_m, rest_k = (m + 127) // 128, n // 64
+        sf_perm = torch.empty((l, rest_m, rest_k, 32, 4, 4), dtype=torch.uint8, device=dev)
+        epi.output = _lib.OUT_NVFP4
+        epi.out_packed, epi.out_sf, epi.out_sf_perm = packed.data_ptr(), sf.data_ptr(), sf_perm.data_ptr()
+        epi.out_packed_row_stride, epi.out_packed_batch_stride = n // 2, m * (n // 2)
+        epi.out_sf_row_stride, epi.out_sf_batch_stride = n // 16, m * (n // 16)
+        epi.out_sf_perm_batch_stride = rest_m * rest_k * 512
+        out = (packed.permute(1, 2, 0).view(FP4_DTYPE), sf.permute(1, 2, 0).view(SF_DTYPE),
+               sf_perm.permute(3, 4, 1, 5, 2, 0).view(SF_DTYPE))
+    cfg = GemmConfig(tile_n, 0, grid, cta_group, split_k)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    with torch.cuda.device(dev):
+        _lib.check(lib.nvfp4_gemm_epilogue(problem, cfg, epi, stream))
+    return out
+
+
 def check_scale_layouts(data: input_t) -> None:
     """Validate that the plain and the permuted scale tensors of one operator call say the same
     (the harness passes both, template.py:11-14; the GEMM reads the permuted ones, the GEMV the
@@ -133,6 +182,14 @@ def check_scale_layouts(data: input_t) -> None:
             row = (first // (k // 16)) % rows
             batch = first // (k // 16) // rows
             raise ValueError(f"{name} and {name}_permuted differ in {bad} scale(s); first at row {row}, scale column {col}, batch {batch}")
+
+
+def release_stream(stream=None) -> None:
+    """Give back the scratch set the GEMM keeps for ``stream`` (default: the current stream), once
+    none of its GEMMs is in flight and no graph captured on it will be replayed again."""
+    lib = _lib.load()
+    stream = stream if stream is not None else torch.cuda.current_stream()
+    _lib.check(lib.nvfp4_release_stream(stream.cuda_stream))
 
 
 def check_status() -> None:

@@ -4,10 +4,12 @@
  * baseline use it as the checker / the timed host baseline; the product never
  * links or calls it.
  *
- * PARITY UNPINNED by reference fixtures (the reference has no CPU code, golden
- * vectors or tests for this path; its ref_kernel lives in a harness file that
- * task.yml:5 names but the repository does not contain).  The arithmetic follows
- * the operator's definition: dequantise e2m1 x e4m3 to fp32, accumulate in fp32
+ * PARITY PINNED by outputs of the reference's own code: tests/golden/ref_cublaslt.json
+ * holds what its cuBLASLt submission (sub_cub.py:48-143) produced on a B200 for seeded
+ * inputs, and the tests hold this file to those bits.  (The reference has no CPU code,
+ * golden vectors or tests for this path; its ref_kernel lives in a harness file that
+ * task.yml:5 names but the repository does not contain.)  The arithmetic follows the
+ * operator's definition: dequantise e2m1 x e4m3 to fp32, accumulate in fp32
  * in ascending k, round to fp16 (nearest-even, overflow -> inf).
  *
  * Layout facts followed (paths inside the reference project):

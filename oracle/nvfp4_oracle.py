@@ -103,6 +103,46 @@ def ref_gemm(a, b, sfa, sfb, accumulate="f32") -> np.ndarray:
     return c
 
 
+def ref_gemm_f32(a, b, sfa, sfb) -> np.ndarray:
+    """The accumulator before the fp16 cast: [M, N, L] fp32 (numpy path; small shapes)."""
+    a, b, sfa, sfb = (np.asarray(x, dtype=np.uint8) for x in (a, b, sfa, sfb))
+    M, _, L = a.shape
+    N = b.shape[0]
+    c = np.empty((M, N, L), dtype=np.float32)
+    for l in range(L):
+        c[:, :, l] = dequantize(a[:, :, l], sfa[:, :, l]) @ dequantize(b[:, :, l], sfb[:, :, l]).T
+    return c
+
+
+def ref_epilogue(acc: np.ndarray, bias=None, activation: str = "none") -> np.ndarray:
+    """What the GEMM's extended epilogue computes from the fp32 accumulator [M, N, L]:
+    fp16(act(acc + bias[column])), the bias added in fp32.  No counterpart in the reference
+    (it writes the plain fp16 cast, sub_cub.py:98-104); the definition is this library's."""
+    x = np.asarray(acc, dtype=np.float32)
+    if bias is not None:
+        x = x + np.asarray(bias, dtype=np.float16).astype(np.float32)[None, :, None]
+    if activation == "relu":
+        x = np.maximum(x, np.float32(0))
+    elif activation == "silu":
+        with np.errstate(over="ignore"):
+            x = (x.astype(np.float64) / (1.0 + np.exp(-x.astype(np.float64)))).astype(np.float32)
+    elif activation != "none":
+        raise ValueError(activation)
+    with np.errstate(over="ignore"):
+        return x.astype(np.float16)
+
+
+def ref_requantize(c16: np.ndarray):
+    """NVFP4 form of an fp16 result [M, N, L]: (packed [M, N/2, L], sf [M, N/16, L]), the
+    quantiser's rule (:func:`quantize_rows`) applied to every batch."""
+    M, N, L = c16.shape
+    packed = np.empty((M, N // 2, L), dtype=np.uint8)
+    sf = np.empty((M, N // 16, L), dtype=np.uint8)
+    for l in range(L):
+        packed[:, :, l], sf[:, :, l] = quantize_rows(c16[:, :, l].astype(np.float32))
+    return packed, sf
+
+
 def permuted_sf_offset(row, col, n_kblk):
     """Byte offset of scale (row, col = k/16) inside one batch of the permuted
     layout (ref.txt:31; s_128t.py:42-45,554-562): 512-byte atoms of 128 rows x 4

@@ -90,6 +90,67 @@ def test_largest_reference_test_shape(sub, oracle):
     assert_bit_exact(out[torch.from_numpy(rows).cuda()], exp, what="2304x4608x7168 sampled rows")
 
 
+# The shapes the reference task is timed on (task.yml:53-56), whole output against the oracle.
+@pytest.mark.parametrize("shape", [(128, 7168, 16384, 1), (128, 4096, 7168, 1), (128, 7168, 2048, 1)])
+def test_benchmark_shapes_match_oracle_bit_exact(sub, oracle, shape):
+    from nvfp4_gemm_b200.inputs import generate_input
+    m, n, k, l = shape
+    data = generate_input(m, n, k, l, 1111)
+    data[6].view(torch.int16).fill_(0x7fff)
+    out = sub.custom_kernel(data)
+    sub.check_status()
+    assert_bit_exact(out, expected_fp16(oracle, data), what=f"{shape} {sub.last_kernel()}")
+
+
+def test_largest_configuration_on_one_gpu_sampled(sub, oracle):
+    """8192 x 28672 x 8192, the job the multi-GPU path partitions, whole on one GPU: sampled rows
+    against the oracle over sampled columns (every 128-column block boundary region is hit), and
+    the all-ones canary shows that every element was written."""
+    from nvfp4_gemm_b200.inputs import generate_input
+    m, n, k, l = 8192, 28672, 8192, 1
+    data = generate_input(m, n, k, l, 1111)
+    data[6].view(torch.int16).fill_(0x7fff)
+    out = sub.custom_kernel(data)
+    sub.check_status()
+    assert int((out.view(torch.int16) == 0x7fff).sum().item()) == 0
+    rng = np.random.default_rng(8)
+    rows = np.sort(rng.choice(m, 48, replace=False))
+    cols = np.sort(np.concatenate([rng.choice(n, 1024, replace=False), np.arange(0, n, 3584), np.arange(3583, n, 3584)]))
+    cols = np.unique(cols)
+    a, b, sfa, sfb = oracle.tensors_to_numpy(data)
+    exp = oracle.ref_gemm_c(a[rows], b[cols], sfa[rows], sfb[cols])
+    got = out[torch.from_numpy(rows).cuda()][:, torch.from_numpy(cols).cuda()]
+    assert_bit_exact(got, exp, what="C4 sampled block on one GPU")
+
+
+def test_gemms_on_two_streams_do_not_share_scratch(sub, oracle, lib):
+    """Two persistent GEMMs whose tiles are shared between workers (so both use the partial-tile
+    scratch and the tile counters) overlap on two streams: each stream has its own scratch set, so
+    both results are exact, over several rounds."""
+    from nvfp4_gemm_b200.inputs import generate_input
+    shapes = [(256, 1024, 8192, 1), (384, 768, 6144, 1)]
+    datas = [generate_input(m, n, k, l, 40 + i) for i, (m, n, k, l) in enumerate(shapes)]
+    exps = [expected_fp16(oracle, d) for d in datas]
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    torch.cuda.synchronize()
+    for rnd in range(6):
+        for d in datas:
+            d[6].view(torch.int16).fill_(0x7fff)
+        torch.cuda.synchronize()
+        for s, d in zip(streams, datas):
+            with torch.cuda.stream(s):
+                for _ in range(3):
+                    sub.gemm(d, tile_n=128, epilogue=1, cta_group=1, split_k=1, grid=40)   # stream-K, tiles shared by workers
+        torch.cuda.synchronize()
+        for s in streams:
+            with torch.cuda.stream(s):
+                sub.check_status()
+        for d, e, shp in zip(datas, exps, shapes):
+            assert_bit_exact(d[6], e, what=f"round {rnd} {shp}")
+    for s in streams:
+        assert lib.nvfp4_release_stream(s.cuda_stream) == 0
+
+
 def test_general_scales_within_stated_tolerance(sub, oracle):
     """Arbitrary e4m3 scales and values: not exact any more, must stay inside rtol = atol = 1e-3."""
     from nvfp4_gemm_b200.inputs import generate_input, permute_scale_factors, SF_DTYPE

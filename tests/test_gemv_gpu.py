@@ -32,13 +32,16 @@ def test_gemv_matches_oracle_bit_exact(sub, oracle, shape):
     assert_bit_exact(out, expected_fp16(oracle, data), what=f"gemv {shape}")
 
 
-def test_gemv_benchmark_shape(sub, oracle):
+# config 2 (7168 x 16384, l = 4) and the shapes the reference's GEMV task is timed on (task_gemv.yml:54-57)
+@pytest.mark.parametrize("shape", [(7168, 16384, 4), (7168, 16384, 1), (4096, 7168, 8), (7168, 2048, 4)])
+def test_gemv_benchmark_shapes(sub, oracle, shape):
     from nvfp4_gemm_b200.inputs import generate_input
-    m, k, l = 7168, 16384, 4
+    m, k, l = shape
     data = generate_input(m, 1, k, l, 1111)
+    data[6].view(torch.int16).fill_(0x7fff)
     out = sub.custom_kernel(data)
     torch.cuda.synchronize()
-    assert_bit_exact(out, expected_fp16(oracle, data), what="gemv 7168x16384x4")
+    assert_bit_exact(out, expected_fp16(oracle, data), what=f"gemv {shape}")
 
 
 def test_gemv_general_scales_within_tolerance(sub, oracle):

@@ -125,3 +125,19 @@ def test_bench_roofline_arithmetic_matches_the_stated_work():
         assert shape["sol_us"] > 0
         if "m" in shape:
             assert shape["k"] % 64 == 0 and (shape["n"] == 1 or shape["n"] % 128 == 0)
+
+
+def test_problem_cache_key_covers_strides_and_none_scales():
+    """Same storage seen through two stride layouts gives two distinct problem structs, and a
+    GEMV-only call may leave the permuted scale tensors out."""
+    import torch
+    from nvfp4_gemm_b200 import submission as S
+    from nvfp4_gemm_b200.inputs import generate_input
+    data = generate_input(64, 1, 512, 1, 3, device="cpu")
+    p = S.make_problem(data[:4] + (None, None, data[6]))
+    assert p.sfa_perm is None and p.sfb_perm is None and p.n == 1
+    store = torch.zeros(64 * 512, dtype=torch.uint8)
+    v1 = torch.as_strided(store, (32, 256, 1), (256, 1, 32 * 256))
+    v2 = torch.as_strided(store, (32, 256, 1), (512, 1, 32 * 512))
+    assert v1.data_ptr() == v2.data_ptr() and S._layout_key(v1) != S._layout_key(v2)
+    assert S._layout_key(None) == (0, (), ())

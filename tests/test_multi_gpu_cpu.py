@@ -101,3 +101,14 @@ def test_block_copy_plan_covers_every_foreign_block_once(world):
     with pytest.raises(ValueError):
         plan_block_copies(0, world, n_local, bases[0], bases, "sideways")
     assert best_allgather_mode(2) == "fused" and best_allgather_mode(8) == "push"
+
+
+def test_multicast_binding_is_refused():
+    """The symmetric output must be mapped for plain peer accesses only; a rendezvous handle that
+    reports a multicast address is an error (fake handles: no GPU needed)."""
+    from types import SimpleNamespace
+    from nvfp4_gemm_b200.multi_gpu import check_no_multicast
+    check_no_multicast(SimpleNamespace(multicast_ptr=0))
+    check_no_multicast(SimpleNamespace())                      # torch builds without the attribute
+    with pytest.raises(RuntimeError, match="multicast"):
+        check_no_multicast(SimpleNamespace(multicast_ptr=0x7F0000000000))

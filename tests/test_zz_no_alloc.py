@@ -50,6 +50,32 @@ def test_static_scratch_gemm_matches_the_allocating_entry_point_twice_in_a_row(c
         # same tolerance as the other parity tests: the fp16 bit patterns are equal
         assert torch.equal(ref.view(torch.int16), out.view(torch.int16)), f"call {call}: outputs differ for {shape}"
         assert not torch.isnan(out.float()).any()
+        # a wait that ran out inside this variant is reported through the same status call
+        assert cuda_lib.nvfp4_check_status(torch.cuda.current_stream().cuda_stream) == 0
+
+
+def test_static_scratch_gemm_matches_the_oracle_and_allocates_nothing(cuda_lib, oracle):
+    """The property the entry point exists for: once its first call on the device is over, a call
+    leaves the device's free memory and the library's own scratch accounting exactly as they
+    were -- and the result is the oracle's, bit for bit."""
+    from helpers import assert_bit_exact, expected_fp16
+    from nvfp4_gemm_b200 import _lib
+    from nvfp4_gemm_b200.inputs import generate_input
+    from nvfp4_gemm_b200.submission import make_problem
+
+    stream = torch.cuda.current_stream().cuda_stream
+    data = generate_input(200, 640, 4096, 1, 9)
+    problem = make_problem(data)
+    _lib.check(cuda_lib.nvfp4_gemm_static_scratch(problem, 0, stream))      # first call on the device: one-time set-up
+    torch.cuda.synchronize()
+    data[6].view(torch.int16).fill_(0x7fff)
+    free_before, lib_bytes_before = torch.cuda.mem_get_info()[0], cuda_lib.nvfp4_scratch_bytes()
+    _lib.check(cuda_lib.nvfp4_gemm_static_scratch(problem, 0, stream))
+    _lib.check(cuda_lib.nvfp4_gemm_static_scratch(problem, 5, stream))
+    assert cuda_lib.nvfp4_check_status(stream) == 0
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert cuda_lib.nvfp4_scratch_bytes() == lib_bytes_before
+    assert_bit_exact(data[6], expected_fp16(oracle, data), what="static scratch vs oracle")
 
 
 def test_static_scratch_gemm_rejects_more_workers_than_it_has_slots_for(cuda_lib):
