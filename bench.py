@@ -203,7 +203,8 @@ def main():
                     help="N > 1: how the column blocks are exchanged.  fused = peer stores in the GEMM epilogue; push / pull = "
                          "this library's copy kernel per row panel on a second stream; ce = copy engines; nccl = NCCL + re-layout; "
                          "auto = fused on 2 GPUs, push on more (the measured best of each)")
-    ap.add_argument("--panels", type=int, default=4, help="N > 1: row panels the exchange is pipelined over (all modes but fused)")
+    ap.add_argument("--panels", type=int, default=0, help="N > 1: row panels the exchange is pipelined over (all modes but fused); 0 = the measured best")
+    ap.add_argument("--copy-sms", type=int, default=-1, help="N > 1, push / pull: SMs reserved for the copy kernel (the GEMM runs on the rest); -1 = the measured best")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary per-config table")
     args = ap.parse_args()
@@ -464,114 +465,179 @@ def extra_table(S, generate_input, dev, peaks, gpu_index):
     return out
 
 
+def default_exchange(world):
+    """Measured-best exchange settings per GPU count (B200 / NVSwitch, the 8192 x 28672 x 8192 job):
+    (mode, row panels, SMs given to the copy kernel)."""
+    return {2: ("fused", 4, 0), 4: ("push", 8, 16), 8: ("push", 16, 24)}.get(world, ("push", 8, 16))
+
+
 def bench_column_parallel(args, w, rank, world, dev):
     """`bench.py --gpus N` for N > 1: strong scaling of the one partitioned workload."""
+    import numpy as np
     import torch
     import torch.distributed as dist
     from nvfp4_gemm_b200 import submission as S
     from nvfp4_gemm_b200.inputs import generate_input
     from nvfp4_gemm_b200.multi_gpu import (ColumnParallelGemm, CopyEngineAllGatherGemm, FusedAllGatherGemm, PanelAllGatherGemm,
-                                           best_allgather_mode, plan_shard, shard_inputs, to_device_same_layout)
+                                           plan_shard, shard_inputs, to_device_same_layout)
 
     m, n, k = w["m"], w["n"], w["k"]
     shard = plan_shard(n, world, rank)
     # every rank builds the same full B from the seed and keeps its rows (inputs are synthetic)
     n_sets = 2
-    sets = []
+    sets, host_sets = [], []
     for i in range(n_sets):
         full = generate_input(m, n, k, 1, 1111 + i, device="cpu")
         local = shard_inputs(full, shard)
-        sets.append(tuple(to_device_same_layout(t, dev) if j < 6 else None for j, t in enumerate(local)))
+        host_sets.append([_flat_bytes(t).clone().pin_memory() for t in local[:6]])
+        sets.append(tuple(to_device_same_layout(t, dev) for t in local[:6]) + (None,))
         del full
-    mode = getattr(args, "allgather", "auto")
-    if mode == "auto":
-        mode = best_allgather_mode(world)
-    fused = None
-    panels = max(1, int(getattr(args, "panels", 4)))
-    try:
+    mode, panels, copy_sms = default_exchange(world)
+    if args.allgather != "auto":
+        mode = args.allgather
+    if args.panels > 0:
+        panels = args.panels
+    if args.copy_sms >= 0:
+        copy_sms = args.copy_sms
+
+    def build(mode, nvfp4_out=False):
         if mode == "fused":
-            fused = FusedAllGatherGemm(m, n, k, device=dev)
-        elif mode == "ce":
-            fused = CopyEngineAllGatherGemm(m, n, k, device=dev, panels=panels)
-        elif mode in ("pull", "push"):
-            fused = PanelAllGatherGemm(m, n, k, device=dev, panels=panels, direction=mode)
+            return FusedAllGatherGemm(m, n, k, device=dev)
+        if mode == "ce":
+            return CopyEngineAllGatherGemm(m, n, k, device=dev, panels=panels)
+        if mode in ("pull", "push"):
+            return PanelAllGatherGemm(m, n, k, device=dev, panels=panels, direction=mode, copy_sms=copy_sms, nvfp4_out=nvfp4_out)
+        return None
+
+    note = ""
+    try:
+        plan = build(mode)
     except Exception as e:  # symmetric memory unavailable on this box: use the NCCL path and say so
-        mode = f"nccl ({mode} path unavailable: {str(e)[:120]})"
-    if fused is not None:
-        c_full = [fused.c_full]
+        plan, note, mode = None, f" ({mode} path unavailable: {str(e)[:120]})", "nccl"
+    if plan is not None:
+        c_full = plan.c_full
 
         def step(i):
-            fused(sets[i % n_sets])
+            plan(sets[i % n_sets])
     else:
-        c_full = [torch.empty((1, m, n), dtype=torch.float16, device=dev).permute(1, 2, 0)]
-        plan = ColumnParallelGemm(m, n, k, device=dev, panels=panels)
+        c_full = torch.empty((1, m, n), dtype=torch.float16, device=dev).permute(1, 2, 0)
+        nccl_plan = ColumnParallelGemm(m, n, k, device=dev, panels=panels)
 
         def step(i):
-            plan(sets[i % n_sets], c_full[0])
+            nccl_plan(sets[i % n_sets], c_full)
+
+    def timed(fn, steps):
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / steps
 
     for i in range(args.warmup):
         step(i)
     S.check_status()
+
+    # ---- parity of the gathered result (rank 0): sampled rows x all columns against the CPU oracle
+    step(0)
     torch.cuda.synchronize()
     dist.barrier()
-    torch.cuda.synchronize()
-
     parity = None
-    step(0)                      # every rank takes part in the collective; rank 0 then checks the result
-    torch.cuda.synchronize()
+    rows = np.sort(np.random.default_rng(0).choice(m, 16, replace=False))
     if rank == 0:
-        # sampled rows of the gathered result against the CPU oracle (all N columns, so every
-        # rank's block and the re-layout are covered)
-        import numpy as np
         from oracle import nvfp4_oracle as O
         full = generate_input(m, n, k, 1, 1111, device="cpu")
-        rows = np.sort(np.random.default_rng(0).choice(m, 16, replace=False))
         a_np, b_np, sfa_np, sfb_np = O.tensors_to_numpy(full)
         exp = O.ref_gemm_c(a_np[rows], b_np, sfa_np[rows], sfb_np)
-        got = c_full[0][torch.from_numpy(rows).to(dev)].cpu().numpy()
+        got = c_full[torch.from_numpy(rows).to(dev)].cpu().numpy()
         parity = "bit-exact on 16 sampled rows x all columns" if np.array_equal(got.view(np.uint16), exp.view(np.uint16)) else "MISMATCH"
         del full
     dist.barrier()
 
+    # ---- the timed region: K steps, device time, max over ranks
     sampler = ClockSampler(dev.index)
     sampler.start()
     launches0 = S.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        step(i)
-    e1.record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_per_step = timed(step, args.steps)
     launches = S.launch_count() - launches0
     clocks = sampler.stop()
     S.check_status()
 
-    # GEMM-only time of this rank's block, for the split of compute vs exchange
-    torch.cuda.synchronize()
-    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # ---- end to end: every step copies this rank's six input tensors from pinned host memory and
+    # reads its share of the gathered result (rows [rank*M/g, (rank+1)*M/g) x all N columns) back
+    r0, r1 = rank * m // world, (rank + 1) * m // world
+    c_host = torch.empty(((r1 - r0) * n,), dtype=torch.float16).pin_memory()
+    h2d = sum(t.numel() for t in host_sets[0])
+    d2h = c_host.numel() * 2
+
+    def e2e_step(i):
+        for dst, src in zip(sets[i % n_sets][:6], host_sets[i % n_sets]):
+            _flat_bytes(dst).copy_(src, non_blocking=True)
+        step(i)
+        c_host.copy_(c_full[r0:r1, :, 0].reshape(-1), non_blocking=True)
+
+    for i in range(2):
+        e2e_step(i)
+    e2e_ms = timed(e2e_step, max(3, min(args.steps, 8)))
+
+    # ---- GEMM-only time of this rank's block, for the split of compute vs exchange
     gemm_only_c = torch.empty((1, m, shard.n_local), dtype=torch.float16, device=dev).permute(1, 2, 0)
     local = sets[0][:6] + (gemm_only_c,)
     S.custom_kernel(local)
-    g0.record()
-    for _ in range(5):
-        S.custom_kernel(local)
-    g1.record()
-    torch.cuda.synchronize()
-    gemm_ms = torch.tensor([g0.elapsed_time(g1) / 5], device=dev)
-    dist.all_reduce(gemm_ms, op=dist.ReduceOp.MAX)
+    gemm_ms = timed(lambda i: S.custom_kernel(local), 5)
+    del local, gemm_only_c
 
-    # The same whole job on ONE GPU of this box (rank 0, the others idle): the strong-scaling
-    # denominator, measured beside the multi-GPU number.
+    # ---- the same exchange with the result re-quantised to NVFP4 in the GEMM's epilogue
+    # (packed e2m1 + permuted scales: 0.5625 bytes per element over NVLink instead of 2)
+    q_ms, q_parity = None, None
+    if plan is not None and not args.no_extra:
+        del plan
+        try:
+            qplan = PanelAllGatherGemm(m, n, k, device=dev, panels=panels, direction="push", copy_sms=copy_sms, nvfp4_out=True)
+            for i in range(3):
+                qplan(sets[i % n_sets])
+            torch.cuda.synchronize()
+            dist.barrier()
+            if rank == 0:
+                from oracle import nvfp4_oracle as O
+                packed, perm = qplan.result()
+                full = generate_input(m, n, k, 1, 1111 + 2 % n_sets, device="cpu")
+                a_np, b_np, sfa_np, sfb_np = O.tensors_to_numpy(full)
+                c16 = O.ref_gemm_c(a_np[rows], b_np, sfa_np[rows], sfb_np)
+                exp_packed, exp_sf = O.ref_requantize(c16)
+                got_packed = packed.view(torch.uint8)[torch.from_numpy(rows).to(dev)].cpu().numpy()
+                perm_flat = torch.as_strided(perm.view(torch.uint8), (perm.numel(),), (1,)).cpu().numpy()
+                sf_cols = n // 16
+                got_sf = np.empty((len(rows), sf_cols, 1), dtype=np.uint8)
+                cols = np.arange(sf_cols)
+                for ri, r in enumerate(rows):
+                    got_sf[ri, :, 0] = perm_flat[O.permuted_sf_offset(int(r), cols, n // 64)]
+                ok = np.array_equal(got_packed, exp_packed) and np.array_equal(got_sf, exp_sf)
+                q_parity = "bit-exact on 16 sampled rows (packed values and scales)" if ok else "MISMATCH"
+                del full
+            dist.barrier()
+            q_ms = timed(lambda i: qplan(sets[i % n_sets]), max(3, min(args.steps, 10)))
+            S.check_status()
+            del qplan
+        except Exception as e:  # noqa: BLE001
+            q_parity = f"not run: {str(e)[:160]}"
+
+    # ---- the same whole job on ONE GPU of this box (rank 0, the others idle): the strong-scaling
+    # denominator, measured beside the multi-GPU number
     one_gpu_ms = None
+    torch.cuda.empty_cache()
     if rank == 0:
-        del local, gemm_only_c
         whole = [generate_input(m, n, k, 1, 1111 + i, device=dev) for i in range(2)]
         for d in whole:
             S.custom_kernel(d)
         torch.cuda.synchronize()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         g0.record()
         for i in range(6):
             S.custom_kernel(whole[i % 2])
@@ -582,38 +648,47 @@ def bench_column_parallel(args, w, rank, world, dev):
     dist.barrier()
 
     if rank == 0:
-        ms_per_step = float(ms.item()) / args.steps
         flops = algorithmic_flops(w)
         tflops = flops / (ms_per_step * 1e-3) / 1e12
         gather_bytes = (world - 1) / world * m * n * 2
+        how = {"ce": "column blocks pushed to the peers by copy engine per row panel, overlapping the next panel's GEMM",
+               "pull": f"each rank pulls the other ranks' column blocks per row panel ({panels} panels) with its own copy kernel (loads over NVLink), overlapping the next panel's GEMM",
+               "push": f"each rank pushes its column block to the peers per row panel ({panels} panels) with its own copy kernel (stores over NVLink) on {copy_sms} SMs of its own, the GEMM on the rest",
+               "fused": "all-gather fused into the GEMM epilogue (peer stores over NVLink)",
+               "nccl": f"NCCL all-gather of fp16 blocks + re-layout, {panels} row panels{note}"}[mode]
         line = dict(metric="nvfp4_matmul_throughput", value=tflops, unit="TFLOP/s", n_gpus=world, steps=args.steps,
                     warmup=args.warmup, ms_per_step=ms_per_step, higher_is_better=True, scaling="strong", vs_baseline=None,
                     dtype="e2m1 x ue4m3 -> f32 -> f16", data="synthetic",
-                    config=dict(workload=w["name"], parallelism=(f"column-parallel over N on {world} GPUs; column blocks pushed to the peers by copy engine per row panel, overlapping the next panel's GEMM"
-                                             if mode == "ce" else
-                                             f"column-parallel over N on {world} GPUs; each rank pulls the other ranks' column blocks per row panel with its own copy kernel (loads over NVLink), overlapping the next panel's GEMM"
-                                             if mode == "pull" else
-                                             f"column-parallel over N on {world} GPUs; each rank pushes its column block to the peers per row panel ({panels} panels) with its own copy kernel (stores over NVLink), overlapping the next panel's GEMM"
-                                             if mode == "push" else
-                                             f"column-parallel over N on {world} GPUs; all-gather fused into the GEMM epilogue (peer stores over NVLink)"
-                                             if fused is not None else
-                                             f"column-parallel over N on {world} GPUs, NCCL all-gather of fp16 blocks, {panels} row panels, {mode}"),
-                                timing="CUDA events, max over ranks; 2 rotating input sets (302 MB per rank set) > L2",
-                                gemm_only_ms_per_rank=float(gemm_ms.item()),
+                    config=dict(workload=w["name"], parallelism=f"column-parallel over N on {world} GPUs; {how}",
+                                timing="CUDA events, max over ranks; 2 rotating input sets per rank > L2",
+                                note="the N = 1 line of this bench is a different workload (the decode GEMM): ratios of this line's value to it are not a scaling curve; "
+                                     "one_gpu_same_job_ms is this job on one GPU of the same box",
+                                gemm_only_ms_per_rank=gemm_ms,
                                 one_gpu_same_job_ms=one_gpu_ms,
                                 speedup_over_one_gpu=(one_gpu_ms / ms_per_step) if one_gpu_ms else None,
-                                gemm_only_tflops_per_gpu=flops / world / (float(gemm_ms.item()) * 1e-3) / 1e12,
+                                gemm_only_tflops_per_gpu=flops / world / (gemm_ms * 1e-3) / 1e12,
                                 allgather_bytes_in_per_gpu=gather_bytes, parity_vs_oracle=parity,
-                                nvlink_bound_ms=gather_bytes / 770e9 * 1e3),
+                                nvlink_bound_ms=gather_bytes / 770e9 * 1e3,
+                                nvfp4_output_exchange=dict(ms_per_step=q_ms, parity_vs_oracle=q_parity,
+                                                           bytes_in_per_gpu=(world - 1) / world * m * n * 0.5625,
+                                                           speedup_over_one_gpu=(one_gpu_ms / q_ms) if (one_gpu_ms and q_ms) else None,
+                                                           what="same job, result re-quantised to NVFP4 in the GEMM epilogue and exchanged in that form (push)")),
                     roofline=dict(bound="nvlink", achieved=gather_bytes / (ms_per_step * 1e-3) / 1e9, peak=770.0, unit="GB/s",
                                   frac=gather_bytes / (ms_per_step * 1e-3) / 1e9 / 770.0, traffic=None,
                                   peak_source="measured peer copy per direction"),
-                    e2e=dict(value=tflops, unit="TFLOP/s", ms_per_step=ms_per_step, h2d_bytes_per_step=0, d2h_bytes_per_step=0,
-                             note="inputs resident; the gathered fp16 C (all N columns) is the step's result on every rank"),
+                    e2e=dict(value=flops / (e2e_ms * 1e-3) / 1e12, unit="TFLOP/s", ms_per_step=e2e_ms, h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
+                             note="per rank and step: the six input tensors from pinned host memory, and the rank's 1/g of the rows of the gathered fp16 C back to the host"),
                     gpu_launches=int(launches), clocks=clocks)
         print(json.dumps(line), flush=True)
     dist.barrier()
     dist.destroy_process_group()
+
+
+def _flat_bytes(t):
+    """A dense (possibly permuted) tensor as its flat bytes, for layout-preserving copies."""
+    import torch
+    raw = t.view(torch.uint8) if t.element_size() == 1 else t
+    return torch.as_strided(raw, (t.numel(),), (1,), raw.storage_offset())
 
 
 if __name__ == "__main__":

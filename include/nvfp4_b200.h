@@ -62,6 +62,7 @@ typedef struct nvfp4_gemm_config {
     int32_t grid;      /* 0 auto (one CTA per SM), else number of persistent CTAs */
     int32_t cta_group; /* 0 auto, 1 = one CTA per tile, 2 = CTA pair per 256-row tile */
     int32_t split_k;   /* 0 auto, 1 = persistent stream-K kernel, 2, 4 or 8 = cluster split-K (reduce in DSMEM; 8 needs tile_n 256) */
+    int32_t raster;    /* tile order of the persistent kernels: 0 auto, -1 = row-major, r > 0 = column-major inside groups of r row tiles */
 } nvfp4_gemm_config;
 
 /*
@@ -110,6 +111,8 @@ typedef struct nvfp4_epilogue {
     int64_t out_packed_row_stride, out_packed_batch_stride; /* bytes; row stride a multiple of 16 */
     int64_t out_sf_row_stride, out_sf_batch_stride;         /* bytes; row stride even */
     int64_t out_sf_perm_batch_stride;                       /* bytes */
+    int64_t out_sf_perm_block_stride;                       /* bytes between 128-row blocks of out_sf_perm; 0 = (n/64)*512 (dense).
+                                                               Larger when this GEMM writes a column block of a wider matrix's scales. */
 } nvfp4_epilogue;
 
 /*
@@ -158,11 +161,14 @@ int nvfp4_gemm_allgather(const nvfp4_problem* problem, const nvfp4_gemm_config* 
  * block): "pull" reads the blocks other GPUs computed into the same place of the local output,
  * "push" writes this GPU's block (every src_blocks[i] the same local pointer) into the peers'
  * outputs.  Plain coalesced 16-byte loads (eight in flight per thread) and stores; ctas = 0 picks
- * two CTAs per SM.  The caller orders it after the producers' kernels (event or cross-rank
- * barrier).  No counterpart in the reference (single GPU).
+ * two CTAs per SM.  own_sms != 0 keeps the copy's CTAs off SMs whose shared memory a persistent
+ * GEMM of this library fills (launch that GEMM with cfg.grid below the SM count and the copy gets
+ * the SMs it leaves free, instead of competing with it for issue slots).  Any byte matrix can be
+ * moved by counting two bytes as one element.  The caller orders it after the producers' kernels
+ * (event or cross-rank barrier).  No counterpart in the reference (single GPU).
  */
 int nvfp4_copy_column_blocks(void* const* dst_blocks, const void* const* src_blocks, int32_t n_blocks, int64_t row0, int64_t rows,
-                             int32_t n_local, int64_t row_stride, int32_t ctas, void* stream);
+                             int32_t n_local, int64_t row_stride, int32_t ctas, int32_t own_sms, void* stream);
 
 /*
  * Strided device-to-device copy (one cudaMemcpy2DAsync: `rows` pieces of `width_bytes`), used to
@@ -281,6 +287,16 @@ int nvfp4_selftest_bounded_wait(void* stream);
  * slot it publishes its first segment to if that segment covers only part of a tile's k-range.
  */
 int nvfp4_plan_units(int total_units, int grid, int cta, int* begin, int* end, int* first_tile_slot, int k_tiles);
+
+/*
+ * Host-side view of the persistent GEMM's tile order (no GPU needed): which output tile (batch,
+ * row tile, column tile) the `tile`-th entry of the workers' linear tile sequence is.  The order
+ * is chosen so that the tiles the workers process at the same time are neighbours in the output
+ * and share operand blocks through L2 (raster_rows row tiles per group, as nvfp4_gemm_config.raster;
+ * 0 = plain row-major order); every output tile appears exactly once.
+ */
+int nvfp4_plan_tile(int total_units, int workers, int k_tiles, int tiles_m, int tiles_n, int raster_rows, int tile, int* batch,
+                    int* row_tile, int* col_tile);
 
 /* Bytes of device scratch the library holds on the current device (0 before the first GEMM). */
 size_t nvfp4_scratch_bytes(void);

@@ -22,7 +22,7 @@ EXPORTED_SYMBOLS = (
     "nvfp4_shutdown", "nvfp4_last_error", "nvfp4_version", "nvfp4_plan_units", "nvfp4_gemm_static_scratch",
     "nvfp4_interleave_column_blocks", "nvfp4_permute_scales", "nvfp4_gemm_allgather", "nvfp4_quantize", "nvfp4_copy_2d", "nvfp4_copy_column_blocks",
     "nvfp4_unpermute_scales", "nvfp4_compare_scale_layouts", "nvfp4_gemv_config", "nvfp4_release_stream",
-    "nvfp4_gemm_epilogue",
+    "nvfp4_gemm_epilogue", "nvfp4_plan_tile",
 )
 
 ACT_NONE, ACT_RELU, ACT_SILU = 0, 1, 2
@@ -53,7 +53,7 @@ class Problem(ctypes.Structure):
 class GemmConfig(ctypes.Structure):
     """Mirror of ``struct nvfp4_gemm_config``."""
     _fields_ = [("tile_n", c_int32), ("epilogue", c_int32), ("grid", c_int32), ("cta_group", c_int32),
-                ("split_k", c_int32)]
+                ("split_k", c_int32), ("raster", c_int32)]
 
 
 class Epilogue(ctypes.Structure):
@@ -63,7 +63,7 @@ class Epilogue(ctypes.Structure):
         ("out_packed", c_void_p), ("out_sf", c_void_p), ("out_sf_perm", c_void_p),
         ("out_packed_row_stride", c_int64), ("out_packed_batch_stride", c_int64),
         ("out_sf_row_stride", c_int64), ("out_sf_batch_stride", c_int64),
-        ("out_sf_perm_batch_stride", c_int64),
+        ("out_sf_perm_batch_stride", c_int64), ("out_sf_perm_block_stride", c_int64),
     ]
 
 
@@ -94,7 +94,7 @@ def load() -> ctypes.CDLL:
     lib.nvfp4_compare_scale_layouts.argtypes = [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int64, c_int64, c_int64, c_void_p, c_void_p]
     lib.nvfp4_compare_scale_layouts.restype = c_int
     lib.nvfp4_copy_column_blocks.argtypes = [ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int32, c_int64, c_int64, c_int32,
-                                             c_int64, c_int32, c_void_p]
+                                             c_int64, c_int32, c_int32, c_void_p]
     lib.nvfp4_copy_column_blocks.restype = c_int
     lib.nvfp4_copy_2d.argtypes = [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p]
     lib.nvfp4_copy_2d.restype = c_int
@@ -121,6 +121,8 @@ def load() -> ctypes.CDLL:
     lib.nvfp4_plan_units.argtypes = [c_int, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int),
                                      ctypes.POINTER(c_int), c_int]
     lib.nvfp4_plan_units.restype = c_int
+    lib.nvfp4_plan_tile.argtypes = [c_int] * 7 + [ctypes.POINTER(c_int)] * 3
+    lib.nvfp4_plan_tile.restype = c_int
     lib.nvfp4_launch_count.argtypes = []
     lib.nvfp4_launch_count.restype = c_uint64
     lib.nvfp4_last_kernel.argtypes = []

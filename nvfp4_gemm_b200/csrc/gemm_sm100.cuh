@@ -79,17 +79,15 @@ struct GemmParams {
     long long out_packed_row_stride, out_packed_batch_stride;   // bytes
     long long out_sf_row_stride, out_sf_batch_stride;           // bytes
     long long out_sf_perm_batch_stride;                         // bytes
+    long long out_sf_perm_block_stride;                         // bytes between 128-row blocks of the permuted scales
     float* scratch;      // partial-tile slots [worker][head|tail][cta of pair][BN/4][128][4] fp32
     int* counters;       // [worker][cta of pair] k-tiles published per shared tile; zero between launches
     int* status;         // host-visible status word
     long long c_row_stride, c_batch_stride;        // elements
     unsigned long long timeout_cycles;  // limit of every in-kernel wait, in SM clock cycles
-#ifdef NVFP4_TRACE
-    unsigned long long* trace;  // [grid][16] cycle counters (development builds only)
-    int dbg_flags;              // 1: skip scale copies, 2: skip MMA and copies, 4: skip scale loads
-#endif
     int M, N, K, L;
     int tiles_m, tiles_n, k_tiles;  // tiles of (128*CG) x BN; k_tiles = K / 256
+    int raster_rows;                // row tiles per group of the persistent kernels' tile order; 0 = row-major
     int total_units;                // tiles_m * tiles_n * L * k_tiles
 };
 
@@ -140,6 +138,38 @@ __host__ __device__ inline int unit_owner(int u, int n, int total_units) {
     while (c > 0 && unit_boundary(c, n, total_units) > u) --c;
     return c;
 }
+// Where tile `tile` of the workers' linear tile sequence lies in the output: (batch, row tile,
+// column tile).  Worker w walks the contiguous tile indices of its unit range, so at any moment
+// the workers sit at the same RELATIVE position r in their ranges.  Tiles are therefore ranked by
+// (r, w): the tiles the workers process at the same time get consecutive ranks, and consecutive
+// ranks fill the output column by column inside groups of raster_rows row tiles -- a wave of
+// workers shares a few row blocks of A and a few column tiles of B through L2 instead of every
+// worker streaming its own pair from DRAM.
+// raster_rows = 0 keeps the plain row-major order of the linear tile index.
+struct TileCoord {
+    int l, mt, nt;
+};
+__host__ __device__ inline TileCoord tile_coords(int tile, int n_workers, int k_tiles, int total_units, int tiles_m, int tiles_n,
+                                                 int raster_rows) {
+    if (raster_rows <= 0) return TileCoord{tile / (tiles_n * tiles_m), (tile / tiles_n) % tiles_m, tile % tiles_n};
+    const int tiles = total_units / k_tiles;
+    const int q = tiles / n_workers;                       // every worker starts q or q + 1 tiles
+    const int w = unit_owner(tile * k_tiles, n_workers, total_units);
+    const int first = (unit_boundary(w, n_workers, total_units) + k_tiles - 1) / k_tiles;   // first tile that starts in w's range
+    const int r = tile - first;
+    const int rank = (r < q) ? r * n_workers + w : q * n_workers + (first - q * w);
+    const int per_batch = tiles_m * tiles_n;
+    TileCoord c;
+    c.l = rank / per_batch;
+    const int x = rank - c.l * per_batch;
+    const int group = x / (raster_rows * tiles_n);
+    const int y = x - group * (raster_rows * tiles_n);
+    const int rows = min(raster_rows, tiles_m - group * raster_rows);
+    c.nt = y / rows;
+    c.mt = group * raster_rows + (y - c.nt * rows);
+    return c;
+}
+
 // Scratch slot of a worker's partial segment: a worker has at most one segment that starts
 // inside a tile ("head", k0 > 0) and at most one that starts a tile but does not finish it.
 __host__ __device__ inline int partial_slot(int worker, int k0, int cg, int cta_rank) {
@@ -259,16 +289,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
     const int u_begin = (KS > 1) ? (worker / KS) * KT + (ks_rank * KT) / KS : unit_boundary(worker, n_workers, p.total_units);
     const int u_end = (KS > 1) ? (worker / KS) * KT + ((ks_rank + 1) * KT) / KS : unit_boundary(worker + 1, n_workers, p.total_units);
     const uint64_t timeout = p.timeout_cycles;
-#ifdef NVFP4_TRACE
-    const long long trace_t_start = clock64();
-    const uint64_t trace_ns_start = ptx::globaltimer_ns();
-    long long trace_wait = 0, trace_wait2 = 0;
-#define NVFP4_TRACE_BEGIN() const long long trace_t0 = clock64()
-#define NVFP4_TRACE_END(acc) acc += clock64() - trace_t0
-#else
-#define NVFP4_TRACE_BEGIN()
-#define NVFP4_TRACE_END(acc)
-#endif
 
     // Warps 0 and 1 run their loops with all 32 lanes converged and hand the single-thread
     // instructions (TMA, tcgen05) to one lane chosen by elect.sync: the compiler then knows the
@@ -281,51 +301,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
         const uint64_t pol_b = (p.tiles_m * CG <= 2) ? ptx::policy_evict_first() : ptx::policy_evict_last();
         uint32_t stage = 0, phase = 0;
         bool ok = true;
-#ifdef NVFP4_TRACE
-        int trace_prod_it = 0;
-#endif
         for (int u = u_begin; u < u_end && ok;) {
             const int tile = u / KT;
             const int k0 = u - tile * KT;
             const int k1 = min(KT, k0 + (u_end - u));
-            const int nb = tile % p.tiles_n;
-            const int mb = ((tile / p.tiles_n) % p.tiles_m) * CG + cta_rank;  // 128-row block of this CTA
-            const int l = tile / (p.tiles_n * p.tiles_m);
+            const TileCoord tc = tile_coords(tile, n_workers, KT, p.total_units, p.tiles_m, p.tiles_n, (KS > 1) ? 0 : p.raster_rows);
+            const int nb = tc.nt;
+            const int mb = tc.mt * CG + cta_rank;  // 128-row block of this CTA
+            const int l = tc.l;
             for (int kt = k0; kt < k1; ++kt) {
                 {
-                    NVFP4_TRACE_BEGIN();
                     ok = ptx::mbar_wait_bounded(bar_empty + stage * 8, phase ^ 1u, abort_flag, timeout);
                     ok = __all_sync(0xffffffffu, ok);
-                    NVFP4_TRACE_END(trace_wait);
                 }
                 if (!ok) break;
-#ifdef NVFP4_TRACE
-                const bool trace_fake = (p.dbg_flags & 8) && trace_prod_it >= STAGES;   // no loads after the first lap
-                const bool trace_no_b = (p.dbg_flags & 16) != 0;
-                ++trace_prod_it;
-                if (trace_fake) {
-                    if (ptx::elect_one() && (CG == 1 || leader)) ptx::mbar_arrive(bar_full + stage * 8);
-                } else if (trace_no_b) {
-                    if (ptx::elect_one()) {
-                        const uint32_t sa = smem_base + stage * S::kStageBytes;
-                        const uint32_t ssfa = sa + S::kABytes + S::kBBytes;
-                        const uint32_t ssfb = ssfa + S::kSfaBytes;
-                        if constexpr (CG == 1) {
-                            const uint32_t full = bar_full + stage * 8;
-                            ptx::mbar_expect_tx(full, S::kStageBytes - S::kBBytes);
-                            ptx::tma_load_3d(sa, &p.tma_a, kt * kBKBytes, mb * kBM, l, full, pol_a);
-                            ptx::tma_load_4d(ssfa, &p.tma_sfa, 0, kt * kMmaPerStage, mb, l, full);
-                            ptx::tma_load_4d(ssfb, &p.tma_sfb, 0, kt * kMmaPerStage, nb * (BN / 128), l, full);
-                        } else {
-                            const uint32_t full = ptx::mapa_u32(bar_full + stage * 8, 0);
-                            if (leader) ptx::mbar_expect_tx(bar_full + stage * 8, 2 * (S::kStageBytes - S::kBBytes));
-                            ptx::tma_load_3d_pair(sa, &p.tma_a, kt * kBKBytes, mb * kBM, l, full, pol_a);
-                            ptx::tma_load_4d_pair(ssfa, &p.tma_sfa, 0, kt * kMmaPerStage, mb, l, full);
-                            ptx::tma_load_4d_pair(ssfb, &p.tma_sfb, 0, kt * kMmaPerStage, nb * (BN / 128), l, full);
-                        }
-                    }
-                } else
-#endif
                 if (ptx::elect_one()) {
                     const uint32_t sa = smem_base + stage * S::kStageBytes;
                     const uint32_t sb = sa + S::kABytes;
@@ -355,9 +344,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
             }
             u += k1 - k0;
         }
-#ifdef NVFP4_TRACE
-        if (lane == 0) p.trace[blockIdx.x * 16 + 1] = trace_wait;
-#endif
     } else if (warp == 1) {
         if (leader) {
             // ------------------------------------------------------ MMA issuer
@@ -375,91 +361,82 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                 const uint32_t empty_bar = bar_acc_empty + (kAccOverlap ? 0u : acc * 8);
                 const uint32_t empty_phase = kAccOverlap ? (acc_it & 1u) : ((acc_it / kNumAcc) & 1u);
                 {
-                    NVFP4_TRACE_BEGIN();
                     ok = ptx::mbar_wait_bounded(empty_bar, empty_phase ^ 1u, abort_flag, timeout);
                     ok = __all_sync(0xffffffffu, ok);
-                    NVFP4_TRACE_END(trace_wait2);
                 }
                 if (!ok) break;
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * S::kAccStride;
-                for (int kt = k0; kt < k1; ++kt) {
-                    {
-                        NVFP4_TRACE_BEGIN();
-                        ok = ptx::mbar_wait_bounded(bar_full + stage * 8, phase, abort_flag, timeout);
-                        ok = __all_sync(0xffffffffu, ok);
-                        NVFP4_TRACE_END(trace_wait);
-                    }
+                // When the slot after the next one to consume has landed too, both are issued as one
+                // group: one wait / vote / fence, one elected issue region and one pair of commits
+                // cover eight MMAs.  A tcgen05.commit holds up the issuing thread for about 90
+                // cycles and the wait-vote-fence sequence for as long again, which on top of the
+                // 12 + 4 instructions of a 256-wide stage exceeds the 512 cycles its MMAs run.  The
+                // second slot is only probed, never waited for: when the loads are just in time
+                // (the usual case in steady state) the stages are issued one by one.
+                for (int kt = k0; kt < k1;) {
+                    const uint32_t stage2 = (stage + 1 == STAGES) ? 0u : stage + 1;
+                    const uint32_t phase2 = (stage + 1 == STAGES) ? phase ^ 1u : phase;
+                    ok = ptx::mbar_wait_bounded(bar_full + stage * 8, phase, abort_flag, timeout);
+                    const bool second = (kt + 1 < k1) && ptx::mbar_test_wait(bar_full + stage2 * 8, phase2);
+                    const int group = __all_sync(0xffffffffu, second) ? 2 : 1;
+                    ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     ptx::tc_fence_after();
                     if (ptx::elect_one()) {
-#ifdef NVFP4_TRACE
-                        if (p.dbg_flags & 2) {  // no tensor work at all: hand the stage straight back
-                            if constexpr (CG == 2) ptx::tc_commit_pair(bar_empty + stage * 8, 0x3);
-                            else ptx::tc_commit(bar_empty + stage * 8);
-                        } else
-#endif
-                        {
-                            const uint32_t sa = smem_base + stage * S::kStageBytes;
-                            const uint32_t sb = sa + S::kABytes;
-                            const uint32_t ssfa = sb + S::kBBytes;
-                            const uint32_t ssfb = ssfa + S::kSfaBytes;
-                            const uint32_t sf_buf = sf_it & 1u;
-                            const uint32_t t_sfa = tmem_base + kSfaCol + sf_buf * 16;
-                            const uint32_t t_sfb = tmem_base + kSfbCol + sf_buf * (kMmaPerStage * kSfbColsPerMma);
-                            // With cta_group::2 each of these runs in both CTAs of the pair, every CTA
-                            // reading its own shared memory at the same offsets.
-#ifdef NVFP4_TRACE
-                            if (!(p.dbg_flags & 1))
-#endif
 #pragma unroll
-                            for (int kb = 0; kb < kMmaPerStage; ++kb) {
-                                ptx::tc_cp_sf<CG>(t_sfa + kb * 4, ptx::smem_desc_sf(ssfa + kb * kSfAtomBytes));
+                        for (int g = 0; g < 2; ++g) {
+                            if (g < group) {
+                                const uint32_t slot = (g == 0) ? stage : stage2;
+                                const uint32_t sa = smem_base + slot * S::kStageBytes;
+                                const uint32_t sb = sa + S::kABytes;
+                                const uint32_t ssfa = sb + S::kBBytes;
+                                const uint32_t ssfb = ssfa + S::kSfaBytes;
+                                const uint32_t sf_buf = (sf_it + g) & 1u;
+                                const uint32_t t_sfa = tmem_base + kSfaCol + sf_buf * 16;
+                                const uint32_t t_sfb = tmem_base + kSfbCol + sf_buf * (kMmaPerStage * kSfbColsPerMma);
+                                // With cta_group::2 each of these runs in both CTAs of the pair, every CTA
+                                // reading its own shared memory at the same offsets.
 #pragma unroll
-                                for (int h = 0; h < BN / 128; ++h)
-                                    ptx::tc_cp_sf<CG>(t_sfb + kb * kSfbColsPerMma + h * 4,
-                                                      ptx::smem_desc_sf(ssfb + h * S::kSfaBytes + kb * kSfAtomBytes));
-                            }
-                            const uint64_t a_desc = ptx::smem_desc_sw128(sa);
-                            const uint64_t b_desc = ptx::smem_desc_sw128(sb);
+                                for (int kb = 0; kb < kMmaPerStage; ++kb) {
+                                    ptx::tc_cp_sf<CG>(t_sfa + kb * 4, ptx::smem_desc_sf(ssfa + kb * kSfAtomBytes));
 #pragma unroll
-                            for (int kb = 0; kb < kMmaPerStage; ++kb) {
-                                // K advances 64 elements = 32 bytes inside the 128-byte swizzle row: +2 in
-                                // the (address >> 4) field of the descriptors.
-                                ptx::tc_mma_nvf4<CG>(d_tmem, a_desc + 2 * kb, b_desc + 2 * kb, idesc, t_sfa + kb * 4,
-                                                     t_sfb + kb * kSfbColsPerMma, (kt > k0 || kb > 0) ? 1u : 0u);
+                                    for (int h = 0; h < BN / 128; ++h)
+                                        ptx::tc_cp_sf<CG>(t_sfb + kb * kSfbColsPerMma + h * 4,
+                                                          ptx::smem_desc_sf(ssfb + h * S::kSfaBytes + kb * kSfAtomBytes));
+                                }
+                                const uint64_t a_desc = ptx::smem_desc_sw128(sa);
+                                const uint64_t b_desc = ptx::smem_desc_sw128(sb);
+#pragma unroll
+                                for (int kb = 0; kb < kMmaPerStage; ++kb) {
+                                    // K advances 64 elements = 32 bytes inside the 128-byte swizzle row: +2 in
+                                    // the (address >> 4) field of the descriptors.
+                                    ptx::tc_mma_nvf4<CG>(d_tmem, a_desc + 2 * kb, b_desc + 2 * kb, idesc, t_sfa + kb * 4,
+                                                         t_sfb + kb * kSfbColsPerMma, (kt + g > k0 || kb > 0) ? 1u : 0u);
+                                }
                             }
-                            // the stage is reusable (in both CTAs) once these MMAs and copies retire
-                            if constexpr (CG == 2) ptx::tc_commit_pair(bar_empty + stage * 8, 0x3);
-                            else ptx::tc_commit(bar_empty + stage * 8);
-                            if (kt == k1 - 1) {  // last k-tile of the segment: publish the accumulator
-                                if constexpr (CG == 2) ptx::tc_commit_pair(bar_acc_full + acc * 8, 0x3);
-                                else ptx::tc_commit(bar_acc_full + acc * 8);
-                            }
+                        }
+                        // the slots are reusable (in both CTAs) once these MMAs and copies retire
+                        if constexpr (CG == 2) ptx::tc_commit_pair(bar_empty + stage * 8, 0x3);
+                        else ptx::tc_commit(bar_empty + stage * 8);
+                        if (group == 2) {
+                            if constexpr (CG == 2) ptx::tc_commit_pair(bar_empty + stage2 * 8, 0x3);
+                            else ptx::tc_commit(bar_empty + stage2 * 8);
+                        }
+                        if (kt + group == k1) {  // last k-tiles of the segment: publish the accumulator
+                            if constexpr (CG == 2) ptx::tc_commit_pair(bar_acc_full + acc * 8, 0x3);
+                            else ptx::tc_commit(bar_acc_full + acc * 8);
                         }
                     }
                     __syncwarp();
-                    ++sf_it;
-                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    sf_it += group;
+                    for (int g = 0; g < group; ++g)
+                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    kt += group;
                 }
-#ifdef NVFP4_TRACE
-                if ((p.dbg_flags & 2) && ok && ptx::elect_one()) {
-                    if constexpr (CG == 2) ptx::tc_commit_pair(bar_acc_full + acc * 8, 0x3);
-                    else ptx::tc_commit(bar_acc_full + acc * 8);
-                }
-                __syncwarp();
-#endif
                 ++acc_it;
                 u += k1 - k0;
             }
-#ifdef NVFP4_TRACE
-            if (lane == 0) {
-                p.trace[blockIdx.x * 16 + 2] = trace_wait;
-                p.trace[blockIdx.x * 16 + 3] = trace_wait2;
-                p.trace[blockIdx.x * 16 + 0] = clock64() - trace_t_start;
-                p.trace[blockIdx.x * 16 + 7] = ptx::globaltimer_ns() - trace_ns_start;
-            }
-#endif
         }
         // (the second CTA of a pair has nothing to issue: the leader's instructions drive both)
     } else {
@@ -474,21 +451,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
             const int tile = u / KT;
             const int k0 = u - tile * KT;
             const int k1 = min(KT, k0 + (u_end - u));
-            const int nb = tile % p.tiles_n;
-            const int mb = ((tile / p.tiles_n) % p.tiles_m) * CG + cta_rank;
-            const int l = tile / (p.tiles_n * p.tiles_m);
+            const TileCoord tc = tile_coords(tile, n_workers, KT, p.total_units, p.tiles_m, p.tiles_n, (KS > 1) ? 0 : p.raster_rows);
+            const int nb = tc.nt;
+            const int mb = tc.mt * CG + cta_rank;
+            const int l = tc.l;
             const uint32_t acc = acc_it % kNumAcc;
             const uint32_t acc_phase = (acc_it / kNumAcc) & 1u;
             // All 128 epilogue threads take the same branch: the outcome of the wait is agreed on
             // through a barrier, so a thread that gave up cannot strand the others at a later one.
             bool got_acc;
             {
-                NVFP4_TRACE_BEGIN();
                 got_acc = ptx::mbar_wait_bounded(bar_acc_full + acc * 8, acc_phase, abort_flag, timeout);
-                NVFP4_TRACE_END(trace_wait);
             }
             if (!ptx::named_bar_and(2, 128, got_acc)) break;
-            NVFP4_TRACE_BEGIN();
             ptx::tc_fence_after();
             const uint32_t t_acc = tmem_base + acc * S::kAccStride + (static_cast<uint32_t>(quad * 32) << 16);
             // drain order: position p reads chunk (p + first_chunk) mod kChunks, so that the half an
@@ -556,7 +531,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                             *reinterpret_cast<uint16_t*>(p.out_sf + l * p.out_sf_batch_stride + static_cast<long long>(row) * p.out_sf_row_stride + blk) = sf2;
                         if (p.out_sf_perm != nullptr)
                             *reinterpret_cast<uint16_t*>(p.out_sf_perm + l * p.out_sf_perm_batch_stride +
-                                                         (static_cast<long long>(row / 128) * (p.N / 64) + blk / 4) * 512 + (row % 32) * 16 +
+                                                         (row / 128) * p.out_sf_perm_block_stride + (blk / 4) * 512 + (row % 32) * 16 +
                                                          ((row / 32) % 4) * 4 + (blk % 4)) = sf2;
                     }
                 }
@@ -564,7 +539,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
             auto release_acc = [&]() {
                 ptx::tc_fence_before();
                 const uint32_t bar = bar_acc_empty + (kAccOverlap ? 0u : acc * 8);
-                if (CG == 2 && !leader) ptx::mbar_arrive_cluster(bar, 0);
+                if (CG == 2 && !leader) ptx::mbar_arrive_cluster_signal(bar, 0);
                 else ptx::mbar_arrive(bar);
             };
 
@@ -719,12 +694,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                 // they process first) finishes the tile; everyone else publishes an fp32 partial.
                 const int w_first = unit_owner(tile * KT, n_workers, p.total_units);
                 int* counter = p.counters + w_first * CG + cta_rank;
-#ifdef NVFP4_TRACE
-#define NVFP4_MARK(i) if (epi_tid == 0) p.trace[blockIdx.x * 16 + (i)] = clock64() - trace_t_start
-#else
-#define NVFP4_MARK(i)
-#endif
-                NVFP4_MARK(8);
                 if (k0 > 0) {
                     // Publish.  Slot layout [BN/4][128 rows][4] keeps every warp-wide 16-byte access
                     // contiguous (512 bytes) and a 32-column chunk contiguous (16 KB).
@@ -745,7 +714,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                     __threadfence();
                     ptx::named_bar_sync(1, 128);
                     if (epi_tid == 0) atomicAdd(counter, k1 - k0);
-                    NVFP4_MARK(9);
                 } else {
                     // Finish: wait until the rest of the k-range has been published (normally long
                     // ago), pull those partials into the now idle operand ring with bulk copies --
@@ -771,7 +739,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                         if (lane == 0) ptx::bulk_wait_group<0>();  // earlier tile stores of this warp have left shared memory
                     }
                     if (!ptx::named_bar_and(1, 128, ready)) break;
-                    NVFP4_MARK(10);
                     constexpr int kChunksPerTile = BN / 32;
                     constexpr int kSlots = S::kFixSlots;
                     const int n_chunks = kChunksPerTile * n_others;          // chunk q = (column chunk, contributor)
@@ -816,23 +783,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                     }
                     release_acc();
                     if (epi_tid == 0) *counter = 0;
-                    NVFP4_MARK(13);
-#ifdef NVFP4_TRACE
-                    if (epi_tid == 0) p.trace[blockIdx.x * 16 + 14] = n_chunks;
-#endif
                 }
             }
-            NVFP4_TRACE_END(trace_wait2);
             ++acc_it;
             u += k1 - k0;
         }
-#ifdef NVFP4_TRACE
-        if (epi_tid == 0) {
-            p.trace[blockIdx.x * 16 + 4] = trace_wait;
-            p.trace[blockIdx.x * 16 + 5] = trace_wait2;
-            p.trace[blockIdx.x * 16 + 6] = clock64() - trace_t_start;
-        }
-#endif
         if constexpr (TMA_STORE) {
             if (lane == 0) ptx::bulk_wait_group<0>();  // staging must outlive the stores that read it
         }

@@ -83,9 +83,6 @@ struct DeviceCtx {
     int* status_host = nullptr;
     int* status_dev = nullptr;
     size_t scratch_bytes = 0;
-#ifdef NVFP4_TRACE
-    unsigned long long* trace = nullptr;
-#endif
     int max_pairs = -1;  // CTA pairs that can be co-resident (cluster occupancy), queried once
     std::vector<MapEntry> maps;
     bool smem_attr_set[24] = {};
@@ -132,10 +129,6 @@ int ensure_scratch(DeviceCtx* c) {
     CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&c->scratch), kStreamSets * kScratchBytes));
     CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&c->counters), kStreamSets * kMaxCtas * sizeof(int)));
     CUDA_TRY(cudaMemset(c->counters, 0, kStreamSets * kMaxCtas * sizeof(int)));
-#ifdef NVFP4_TRACE
-    CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&c->trace), kMaxCtas * 16 * sizeof(unsigned long long)));
-    CUDA_TRY(cudaMemset(c->trace, 0, kMaxCtas * 16 * sizeof(unsigned long long)));
-#endif
     CUDA_TRY(cudaDeviceSynchronize());
     c->scratch_bytes = kStreamSets * (kScratchBytes + kMaxCtas * sizeof(int));
     return NVFP4_OK;
@@ -407,14 +400,18 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, const nvfp4_
                 return fail(NVFP4_ERR_INVALID_ARGUMENT, "out_sf must be 2-byte aligned with an even row stride >= n/16");
             if (epi->out_sf_perm && !aligned(epi->out_sf_perm, 16))
                 return fail(NVFP4_ERR_INVALID_ARGUMENT, "out_sf_perm must be 16-byte aligned");
-            const long long perm_bytes = static_cast<long long>((p->m + 127) / 128) * (p->n / 64) * 512;
+            if (epi->out_sf_perm && epi->out_sf_perm_block_stride &&
+                (epi->out_sf_perm_block_stride % 16 || epi->out_sf_perm_block_stride < static_cast<long long>(p->n / 64) * 512))
+                return fail(NVFP4_ERR_INVALID_ARGUMENT, "out_sf_perm_block_stride must be 0 or a multiple of 16 that is >= (n/64)*512");
+            const long long block_stride = epi->out_sf_perm_block_stride ? epi->out_sf_perm_block_stride : static_cast<long long>(p->n / 64) * 512;
+            const long long perm_bytes = static_cast<long long>((p->m + 127) / 128 - 1) * block_stride + static_cast<long long>(p->n / 64) * 512;
             if (p->l > 1 && (epi->out_packed_batch_stride % 16 || epi->out_sf_batch_stride % 2 || epi->out_sf_perm_batch_stride % 16 ||
                              (epi->out_sf_perm && epi->out_sf_perm_batch_stride < perm_bytes)))
                 return fail(NVFP4_ERR_INVALID_ARGUMENT, "output batch strides too small or misaligned");
         }
     }
 
-    nvfp4_gemm_config cf = {0, 0, 0, 0, 0};
+    nvfp4_gemm_config cf = {0, 0, 0, 0, 0, 0};
     if (cfg) cf = *cfg;
     if (cf.tile_n != 0 && cf.tile_n != 128 && cf.tile_n != 256)
         return fail(NVFP4_ERR_INVALID_ARGUMENT, "tile_n must be 0, 128 or 256");
@@ -422,6 +419,7 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, const nvfp4_
     if (cf.cta_group < 0 || cf.cta_group > 2) return fail(NVFP4_ERR_INVALID_ARGUMENT, "cta_group must be 0, 1 or 2");
     if (cf.split_k != 0 && cf.split_k != 1 && cf.split_k != 2 && cf.split_k != 4 && cf.split_k != 8)
         return fail(NVFP4_ERR_INVALID_ARGUMENT, "split_k must be 0, 1, 2, 4 or 8");
+    if (cf.raster < -1 || cf.raster > 1024) return fail(NVFP4_ERR_INVALID_ARGUMENT, "raster must be -1 (off), 0 (auto) or a row-tile count");
 
     DeviceCtx* c = nullptr;
     if (int rc = get_ctx(&c)) return rc;
@@ -451,6 +449,13 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, const nvfp4_
     const long long units = static_cast<long long>(g.tiles_m) * g.tiles_n * p->l * g.k_tiles;
     if (units > 0x7fffffffLL) return fail(NVFP4_ERR_INVALID_ARGUMENT, "problem too large: %lld work units", units);
     g.total_units = static_cast<int>(units);
+    // Tile order of the persistent kernels: operands that fit L2 comfortably are read from DRAM
+    // once whatever the order, and the plain order spreads the workers over distinct operand
+    // blocks; larger ones are walked in column-major groups so that a wave of workers shares blocks.
+    {
+        const double operand_bytes = static_cast<double>(p->l) * (static_cast<double>(p->m) + p->n) * (p->k / 2);
+        g.raster_rows = cf.raster > 0 ? cf.raster : (cf.raster == 0 && operand_bytes > 64e6) ? 16 : 0;
+    }
     g.c = static_cast<__half*>(p->c);
     if (epi) {
         g.bias = static_cast<const __half*>(epi->bias);
@@ -465,6 +470,7 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, const nvfp4_
             g.out_sf_row_stride = epi->out_sf_row_stride;
             g.out_sf_batch_stride = epi->out_sf_batch_stride;
             g.out_sf_perm_batch_stride = epi->out_sf_perm_batch_stride;
+            g.out_sf_perm_block_stride = epi->out_sf_perm_block_stride ? epi->out_sf_perm_block_stride : static_cast<long long>(p->n / 64) * 512;
         }
     }
     int set = 0;
@@ -475,10 +481,6 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, const nvfp4_
     g.c_row_stride = p->c_row_stride;
     g.c_batch_stride = p->c_batch_stride;
     g.timeout_cycles = g_timeout_ns.load() * 2;  // SM clock <= 2 GHz: at least the requested time
-#ifdef NVFP4_TRACE
-    g.trace = c->trace;
-    g.dbg_flags = std::getenv("NVFP4_DBG_FLAGS") ? std::atoi(std::getenv("NVFP4_DBG_FLAGS")) : 0;
-#endif
 
     // Whole tiles leave through the TMA-store epilogue unless the caller asks for plain stores.
     int epilogue = cf.epilogue;
@@ -486,10 +488,10 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, const nvfp4_
     if (epi) epilogue = 1;                     // the extended epilogue writes with plain stores
     if (epi && to_nvfp4 && g.out_sf_perm && p->m % 128) {
         // rows of the last 128-row block that do not exist must read as zero scales
-        const long long per_batch = static_cast<long long>((p->m + 127) / 128) * (p->n / 64) * 512;
+        const long long last_block = static_cast<long long>((p->m + 127) / 128 - 1) * g.out_sf_perm_block_stride;
         const long long tail = static_cast<long long>(p->n / 64) * 512;
         for (int l = 0; l < p->l; ++l)
-            CUDA_TRY(cudaMemsetAsync(g.out_sf_perm + l * g.out_sf_perm_batch_stride + per_batch - tail, 0, tail, stream));
+            CUDA_TRY(cudaMemsetAsync(g.out_sf_perm + l * g.out_sf_perm_batch_stride + last_block, 0, tail, stream));
     }
 
     const uint64_t kbytes = static_cast<uint64_t>(p->k) / 2;
@@ -591,7 +593,7 @@ int nvfp4_gemm_allgather(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, v
         if (!c_peers[i] || !aligned(c_peers[i], 16)) return fail(NVFP4_ERR_INVALID_ARGUMENT, "c_peers[%d] must be a 16-byte aligned pointer", i);
     // the cluster split-K kernels (decode shapes) finish tiles in their exchange epilogue, which
     // does know about peers too, but keep this entry on the persistent kernels: one code path
-    nvfp4_gemm_config cf = {0, 0, 0, 0, 0};
+    nvfp4_gemm_config cf = {0, 0, 0, 0, 0, 0};
     if (cfg) cf = *cfg;
     if (cf.split_k == 0) cf.split_k = 1;
     return gemm_impl(p, &cf, nullptr, c_peers, n_peers, stream_v);
@@ -751,7 +753,7 @@ int nvfp4_compare_scale_layouts(const void* plain, const void* permuted, int32_t
 }
 
 int nvfp4_copy_column_blocks(void* const* dst_blocks, const void* const* src_blocks, int32_t n_blocks, int64_t row0, int64_t rows,
-                             int32_t n_local, int64_t row_stride, int32_t ctas, void* stream_v) {
+                             int32_t n_local, int64_t row_stride, int32_t ctas, int32_t own_sms, void* stream_v) {
     if (n_blocks < 1 || n_blocks > 7 || !dst_blocks || !src_blocks) return fail(NVFP4_ERR_INVALID_ARGUMENT, "1..7 blocks required");
     if (rows < 1 || row0 < 0 || n_local < 8 || n_local % 8 || row_stride % 8 || row_stride < n_local)
         return fail(NVFP4_ERR_INVALID_ARGUMENT, "rows >= 1, n_local and row_stride multiples of 8 elements, row_stride >= n_local required");
@@ -768,7 +770,11 @@ int nvfp4_copy_column_blocks(void* const* dst_blocks, const void* const* src_blo
     CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     if (rows * (n_local / 8) * n_blocks >= (1ll << 31)) return fail(NVFP4_ERR_INVALID_ARGUMENT, "more than 2^31 16-byte units in one call");
     int grid = ctas > 0 ? ctas : sms * 2;
-    copy_column_blocks_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream_v)>>>(pp, row0, static_cast<unsigned>(rows),
+    // own_sms: ask for shared memory the kernel never touches, more than a persistent GEMM CTA
+    // leaves free on its SM, so the copy's CTAs are placed on the SMs that GEMM does not occupy
+    // instead of sharing issue slots with it.
+    const size_t reserve = own_sms ? 24 * 1024 : 0;
+    copy_column_blocks_kernel<<<grid, 256, reserve, static_cast<cudaStream_t>(stream_v)>>>(pp, row0, static_cast<unsigned>(rows),
                                                                                      static_cast<unsigned>(n_local / 8), row_stride / 8);
     CUDA_TRY(cudaGetLastError());
     g_launches.fetch_add(1);
@@ -885,16 +891,18 @@ int nvfp4_plan_units(int total_units, int grid, int cta, int* begin, int* end, i
     return NVFP4_OK;
 }
 
-#ifdef NVFP4_TRACE
-int nvfp4_debug_read_trace(unsigned long long* out, int n_ctas) {
-    DeviceCtx* c = nullptr;
-    if (int rc = get_ctx(&c)) return rc;
-    if (!c->trace || n_ctas > kMaxCtas) return fail(NVFP4_ERR_INVALID_ARGUMENT, "no trace buffer");
-    CUDA_TRY(cudaDeviceSynchronize());
-    CUDA_TRY(cudaMemcpy(out, c->trace, static_cast<size_t>(n_ctas) * 16 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+int nvfp4_plan_tile(int total_units, int workers, int k_tiles, int tiles_m, int tiles_n, int raster_rows, int tile, int* batch,
+                    int* row_tile, int* col_tile) {
+    if (total_units < 1 || workers < 1 || k_tiles < 1 || tiles_m < 1 || tiles_n < 1 || total_units % k_tiles || tile < 0 ||
+        tile >= total_units / k_tiles || (total_units / k_tiles) % (tiles_m * tiles_n) || !batch || !row_tile || !col_tile)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "bad tile query");
+    const TileCoord c = tile_coords(tile, workers, k_tiles, total_units, tiles_m, tiles_n, raster_rows);
+    *batch = c.l;
+    *row_tile = c.mt;
+    *col_tile = c.nt;
     return NVFP4_OK;
 }
-#endif
+
 
 uint64_t nvfp4_launch_count(void) { return g_launches.load(); }
 
@@ -911,9 +919,6 @@ void nvfp4_shutdown(void) {
         cudaDeviceSynchronize();
         if (c->scratch) cudaFree(c->scratch);
         if (c->counters) cudaFree(c->counters);
-#ifdef NVFP4_TRACE
-        if (c->trace) cudaFree(c->trace);
-#endif
         if (c->status_host) cudaFreeHost(c->status_host);
         delete c;
         g_ctx[d] = nullptr;

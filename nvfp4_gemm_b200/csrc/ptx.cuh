@@ -44,7 +44,8 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// Arrive on the barrier at the same offset in another CTA of the cluster.
+// Arrive on the barrier at the same offset in another CTA of the cluster, with a cluster-scope
+// release: the peer that acquires the phase sees this thread's earlier writes to its memory.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar, uint32_t cta_rank) {
     asm volatile(
         "{\n\t.reg .b32 remote;\n\t"
@@ -52,11 +53,32 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar, uint32_t cta_r
         "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [remote];\n\t}"
         ::"r"(bar), "r"(cta_rank) : "memory");
 }
+// The same arrival as a pure signal (default semantics: release at CTA scope): for hand-offs
+// that publish no memory of this thread -- e.g. "my tcgen05.ld of the accumulator is complete",
+// which tcgen05.wait::ld and the tcgen05 fences order, not the memory model.  Noticeably
+// cheaper than the cluster-scope release.
+__device__ __forceinline__ void mbar_arrive_cluster_signal(uint32_t bar, uint32_t cta_rank) {
+    asm volatile(
+        "{\n\t.reg .b32 remote;\n\t"
+        "mapa.shared::cluster.u32 remote, %0, %1;\n\t"
+        "mbarrier.arrive.shared::cluster.b64 _, [remote];\n\t}"
+        ::"r"(bar), "r"(cta_rank) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Non-blocking probe of the same condition.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;

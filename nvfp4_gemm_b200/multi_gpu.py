@@ -254,36 +254,59 @@ class CopyEngineAllGatherGemm:
         return self.c_full
 
 
-def plan_block_copies(rank: int, world: int, n_local: int, local_ptr: int, buffer_ptrs, direction: str):
-    """Source and destination addresses of the copy kernel's column blocks (fp16, so a block starts
-    2 * n_local * owner bytes into a row).  The peer order starts with the next rank, so that at any
-    moment the ranks talk to different peers.  Returns (peers, src, dst)."""
+def plan_block_copies(rank: int, world: int, n_local: int, local_ptr: int, buffer_ptrs, direction: str, block_bytes: int = 0):
+    """Source and destination addresses of the copy kernel's column blocks.  A rank's block starts
+    ``block_bytes * owner`` bytes into a row (default: fp16 columns, 2 * n_local).  The peer order
+    starts with the next rank, so that at any moment the ranks talk to different peers.  Returns
+    (peers, src, dst)."""
+    bb = block_bytes or n_local * 2
     peers = [(rank + 1 + i) % world for i in range(world - 1)]
     if direction == "pull":      # the blocks the peers own, from their C into mine
-        src = [buffer_ptrs[r] + r * n_local * 2 for r in peers]
-        dst = [local_ptr + r * n_local * 2 for r in peers]
+        src = [buffer_ptrs[r] + r * bb for r in peers]
+        dst = [local_ptr + r * bb for r in peers]
     elif direction == "push":    # the block I own, from my C into theirs
-        src = [local_ptr + rank * n_local * 2 for _ in peers]
-        dst = [buffer_ptrs[r] + rank * n_local * 2 for r in peers]
+        src = [local_ptr + rank * bb for _ in peers]
+        dst = [buffer_ptrs[r] + rank * bb for r in peers]
     else:
         raise ValueError("direction must be 'push' or 'pull'")
     return peers, src, dst
 
 
+def symmetric_bytes(nbytes: int, device, group):
+    """`nbytes` of symmetric memory (uint8) mapped for plain peer accesses; see symmetric_output."""
+    import os
+    os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"
+    import torch.distributed._symmetric_memory as symm_mem
+    buf = symm_mem.empty((nbytes,), dtype=torch.uint8, device=device)
+    handle = symm_mem.rendezvous(buf, group)
+    check_no_multicast(handle)
+    return buf, handle
+
+
 class PanelAllGatherGemm:
     """Column-parallel GEMM with the exchange done by this library's copy kernel, row panel by row
     panel, on a second stream while the tensor cores work on the next panel.  Every rank runs its
-    GEMM straight into its own columns of the full row-major C (symmetric memory); nothing is
+    GEMM straight into its own columns of the full row-major result (symmetric memory); nothing is
     staged or re-laid-out.
 
     direction="push": after a panel's GEMM (stream order, no cross-rank wait) the copy kernel
-    writes the panel of this rank's column block into every peer's C (stores over NVLink).
+    writes the panel of this rank's column block into every peer's result (stores over NVLink).
     direction="pull": after a panel, a stream-ordered cross-rank barrier tells everyone that this
     panel exists on every rank, and the copy kernel reads the other ranks' blocks of the panel from
-    their peer-mapped C (loads over NVLink).
+    their peer-mapped result (loads over NVLink).
+
+    copy_sms > 0 splits the SMs: the GEMM runs on ``SMs - copy_sms`` persistent CTAs and the copy
+    kernel's CTAs are kept on the SMs it leaves free (they would otherwise share the GEMM's SMs and
+    slow both down).
+
+    nvfp4_out=True: the GEMM's epilogue re-quantises the result to NVFP4 (packed e2m1 + permuted
+    e4m3 scales, the operand form of a following GEMM) and the exchange moves those bytes, 0.5625
+    per element instead of 2.  ``result()`` then returns (packed, sf_permuted) views of the full
+    matrix instead of the fp16 C.
     """
 
-    def __init__(self, m: int, n: int, k: int, group=None, device=None, panels: int = 4, copy_ctas: int = 0, direction: str = "push"):
+    def __init__(self, m: int, n: int, k: int, group=None, device=None, panels: int = 4, copy_ctas: int = 0, direction: str = "push",
+                 copy_sms: int = 0, nvfp4_out: bool = False):
         import ctypes
         if direction not in ("push", "pull"):
             raise ValueError("direction must be 'push' or 'pull'")
@@ -296,41 +319,93 @@ class PanelAllGatherGemm:
         self.shard = plan_shard(n, self.world, self.rank)
         self.m, self.n, self.k = m, n, k
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
-        self.c_sym, self.handle = symmetric_output(m, n, self.device, self.group)
-        self.c_full = self.c_sym.view(1, m, n).permute(1, 2, 0)
         self.panels = row_panels(m, panels)
-        self.copy_ctas = copy_ctas
         self.copy_stream = torch.cuda.Stream(device=self.device)
-        peers, src, dst = plan_block_copies(self.rank, self.world, self.shard.n_local, self.c_sym.data_ptr(),
-                                            [int(p) for p in self.handle.buffer_ptrs], direction)
-        self.src = (ctypes.c_void_p * len(peers))(*src)
-        self.dst = (ctypes.c_void_p * len(peers))(*dst)
-        self.n_blocks = len(peers)
+        self.nvfp4_out = nvfp4_out
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.copy_sms = max(0, min(int(copy_sms), sms - 2))
+        self.gemm_grid = ((sms - self.copy_sms) // 2) * 2 if self.copy_sms else 0
+        self.copy_ctas = self.copy_sms * 8 if self.copy_sms else copy_ctas
+        nl = self.shard.n_local
+        if not nvfp4_out:
+            self.c_sym, self.handle = symmetric_output(m, n, self.device, self.group)
+            self.c_full = self.c_sym.view(1, m, n).permute(1, 2, 0)
+            ptrs = [int(p) for p in self.handle.buffer_ptrs]
+            # (address lists of one copy launch per panel: geometry in fp16 elements)
+            self.copies = [self._copy_plan(self.c_sym.data_ptr(), ptrs, nl * 2, nl, n, rows_scale=1)]
+        else:
+            if m % 128 or nl % 64:
+                raise ValueError("the NVFP4 exchange needs m % 128 == 0 and (n / world) % 64 == 0")
+            self.packed_bytes = m * (n // 2)
+            self.perm_bytes = (m // 128) * (n // 64) * 512
+            self.buf, self.handle = symmetric_bytes(self.packed_bytes + self.perm_bytes, self.device, self.group)
+            ptrs = [int(p) for p in self.handle.buffer_ptrs]
+            base = self.buf.data_ptr()
+            # a byte matrix is moved by counting two bytes as one 16-bit element
+            self.copies = [
+                self._copy_plan(base, ptrs, nl // 2, nl // 4, n // 4, rows_scale=1),                                   # packed rows
+                self._copy_plan(base + self.packed_bytes, [p + self.packed_bytes for p in ptrs], (nl // 64) * 512,
+                                (nl // 64) * 256, (n // 64) * 256, rows_scale=128),                                    # scale atoms, per 128 rows
+            ]
 
-    def __call__(self, local_data) -> torch.Tensor:
+    def _copy_plan(self, local_ptr, buffer_ptrs, block_bytes, n_local_el, row_stride_el, rows_scale):
+        import ctypes
+        peers, src, dst = plan_block_copies(self.rank, self.world, 0, local_ptr, buffer_ptrs, self.direction, block_bytes=block_bytes)
+        return dict(src=(ctypes.c_void_p * len(peers))(*src), dst=(ctypes.c_void_p * len(peers))(*dst), n=len(peers),
+                    n_local=n_local_el, row_stride=row_stride_el, rows_scale=rows_scale)
+
+    def result(self):
+        if not self.nvfp4_out:
+            return self.c_full
+        from .inputs import FP4_DTYPE, SF_DTYPE
+        packed = self.buf[:self.packed_bytes].view(1, self.m, self.n // 2).permute(1, 2, 0).view(FP4_DTYPE)
+        perm = self.buf[self.packed_bytes:].view(1, self.m // 128, self.n // 64, 32, 4, 4).permute(3, 4, 1, 5, 2, 0).view(SF_DTYPE)
+        return packed, perm
+
+    def _gemm_panel(self, lib, local_data, p0, p1, stream):
         from . import _lib
-        from .submission import custom_kernel
-        lib = _lib.load()
+        from .submission import make_problem
         a, b, sfa, sfb, sfa_perm, sfb_perm, _ = local_data
+        rb0, rb1 = p0 // 128, (p1 + 127) // 128
+        cfg = _lib.GemmConfig(0, 0, self.gemm_grid, 0, 0, 0)
+        if not self.nvfp4_out:
+            c_panel = self.c_full[p0:p1, self.shard.begin:self.shard.end]
+            problem = make_problem((a[p0:p1], b, sfa[p0:p1], sfb, sfa_perm[:, :, rb0:rb1], sfb_perm, c_panel))
+            _lib.check(lib.nvfp4_gemm(problem, cfg, stream))
+            return
+        problem = make_problem((a[p0:p1], b, sfa[p0:p1], sfb, sfa_perm[:, :, rb0:rb1], sfb_perm, None))
+        n, nl = self.n, self.shard.n_local
+        epi = _lib.Epilogue()
+        epi.output = _lib.OUT_NVFP4
+        base = self.buf.data_ptr()
+        epi.out_packed = base + p0 * (n // 2) + self.rank * (nl // 2)
+        epi.out_packed_row_stride = n // 2
+        epi.out_sf_perm = base + self.packed_bytes + rb0 * (n // 64) * 512 + self.rank * (nl // 64) * 512
+        epi.out_sf_perm_block_stride = (n // 64) * 512
+        _lib.check(lib.nvfp4_gemm_epilogue(problem, cfg, epi, stream))
+
+    def __call__(self, local_data):
+        from . import _lib
+        lib = _lib.load()
         compute = torch.cuda.current_stream(self.device)
         self.handle.barrier(channel=0)                     # nobody still reads the previous result
         for idx, (p0, p1) in enumerate(self.panels):
-            rb0, rb1 = p0 // 128, (p1 + 127) // 128
-            c_panel = self.c_full[p0:p1, self.shard.begin:self.shard.end]
-            custom_kernel((a[p0:p1], b, sfa[p0:p1], sfb, sfa_perm[:, :, rb0:rb1], sfb_perm, c_panel))
+            self._gemm_panel(lib, local_data, p0, p1, compute.cuda_stream)
             if self.direction == "pull":
                 self.handle.barrier(channel=1 + idx % 2)   # this panel now exists on every rank
             ready = torch.cuda.Event()
             ready.record(compute)
             self.copy_stream.wait_event(ready)
-            _lib.check(lib.nvfp4_copy_column_blocks(self.dst, self.src, self.n_blocks, p0, p1 - p0, self.shard.n_local, self.n,
-                                                    self.copy_ctas, self.copy_stream.cuda_stream))
+            for cp in self.copies:
+                _lib.check(lib.nvfp4_copy_column_blocks(cp["dst"], cp["src"], cp["n"], p0 // cp["rows_scale"], (p1 - p0) // cp["rows_scale"],
+                                                        cp["n_local"], cp["row_stride"], self.copy_ctas, 1 if self.copy_sms else 0,
+                                                        self.copy_stream.cuda_stream))
         done = torch.cuda.Event()
         done.record(self.copy_stream)
         compute.wait_event(done)
         if self.direction == "push":
             self.handle.barrier(channel=1)                 # every rank's blocks have landed here
-        return self.c_full
+        return self.result()
 
 
 def best_allgather_mode(world: int) -> str:

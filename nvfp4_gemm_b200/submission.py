@@ -97,12 +97,12 @@ def custom_kernel(data: input_t) -> output_t:
 
 
 def gemm(data: input_t, tile_n: int = 0, epilogue: int = 0, grid: int = 0, cta_group: int = 0,
-         split_k: int = 0) -> output_t:
+         split_k: int = 0, raster: int = 0) -> output_t:
     """The GEMM with an explicit kernel configuration (tests and tuning)."""
     lib = _lib.load()
     _require_cuda(data)
     problem = make_problem(data)
-    cfg = GemmConfig(tile_n, epilogue, grid, cta_group, split_k)
+    cfg = GemmConfig(tile_n, epilogue, grid, cta_group, split_k, raster)
     stream = torch.cuda.current_stream(data[0].device).cuda_stream
     with torch.cuda.device(data[0].device):
         _lib.check(lib.nvfp4_gemm(problem, cfg, stream))
@@ -150,7 +150,7 @@ def gemm_epilogue(data: input_t, bias=None, activation: str = "none", nvfp4_out:
         epi.out_sf_perm_batch_stride = rest_m * rest_k * 512
         out = (packed.permute(1, 2, 0).view(FP4_DTYPE), sf.permute(1, 2, 0).view(SF_DTYPE),
                sf_perm.permute(3, 4, 1, 5, 2, 0).view(SF_DTYPE))
-    cfg = GemmConfig(tile_n, 0, grid, cta_group, split_k)
+    cfg = GemmConfig(tile_n, 0, grid, cta_group, split_k, 0)
     stream = torch.cuda.current_stream(dev).cuda_stream
     with torch.cuda.device(dev):
         _lib.check(lib.nvfp4_gemm_epilogue(problem, cfg, epi, stream))

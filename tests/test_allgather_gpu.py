@@ -73,7 +73,7 @@ def test_copy_kernel_pulls_the_other_ranks_column_blocks_and_nothing_else(cuda_l
     peers = [r for r in range(blocks) if r != rank]
     src = (ctypes.c_void_p * len(peers))(*[outs[r].data_ptr() + r * n_local * 2 for r in peers])
     dst = (ctypes.c_void_p * len(peers))(*[outs[rank].data_ptr() + r * n_local * 2 for r in peers])
-    _lib.check(cuda_lib.nvfp4_copy_column_blocks(dst, src, len(peers), row0, rows, n_local, n_total, 0, torch.cuda.current_stream().cuda_stream))
+    _lib.check(cuda_lib.nvfp4_copy_column_blocks(dst, src, len(peers), row0, rows, n_local, n_total, 0, 0, torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()
     exp = before.clone()
     for r in peers:
@@ -86,11 +86,11 @@ def test_copy_kernel_rejects_bad_arguments(cuda_lib):
     t = torch.zeros((64, 256), dtype=torch.float16, device="cuda")
     one = (ctypes.c_void_p * 1)(t.data_ptr())
     odd = (ctypes.c_void_p * 1)(t.data_ptr() + 2)
-    assert cuda_lib.nvfp4_copy_column_blocks(one, one, 0, 0, 64, 128, 256, 0, None) == _lib.NVFP4_ERR_INVALID_ARGUMENT
-    assert cuda_lib.nvfp4_copy_column_blocks(one, one, 8, 0, 64, 128, 256, 0, None) == _lib.NVFP4_ERR_INVALID_ARGUMENT
-    assert cuda_lib.nvfp4_copy_column_blocks(one, odd, 1, 0, 64, 128, 256, 0, None) == _lib.NVFP4_ERR_INVALID_ARGUMENT
-    assert cuda_lib.nvfp4_copy_column_blocks(one, one, 1, 0, 64, 100, 256, 0, None) == _lib.NVFP4_ERR_INVALID_ARGUMENT
-    assert cuda_lib.nvfp4_copy_column_blocks(one, one, 1, 0, 64, 512, 256, 0, None) == _lib.NVFP4_ERR_INVALID_ARGUMENT
+    assert cuda_lib.nvfp4_copy_column_blocks(one, one, 0, 0, 64, 128, 256, 0, 0, None) == _lib.NVFP4_ERR_INVALID_ARGUMENT
+    assert cuda_lib.nvfp4_copy_column_blocks(one, one, 8, 0, 64, 128, 256, 0, 0, None) == _lib.NVFP4_ERR_INVALID_ARGUMENT
+    assert cuda_lib.nvfp4_copy_column_blocks(one, odd, 1, 0, 64, 128, 256, 0, 0, None) == _lib.NVFP4_ERR_INVALID_ARGUMENT
+    assert cuda_lib.nvfp4_copy_column_blocks(one, one, 1, 0, 64, 100, 256, 0, 0, None) == _lib.NVFP4_ERR_INVALID_ARGUMENT
+    assert cuda_lib.nvfp4_copy_column_blocks(one, one, 1, 0, 64, 512, 256, 0, 0, None) == _lib.NVFP4_ERR_INVALID_ARGUMENT
 
 
 def test_copy_kernel_pushes_one_block_into_every_peer_output(cuda_lib):
@@ -101,7 +101,7 @@ def test_copy_kernel_pushes_one_block_into_every_peer_output(cuda_lib):
     outs = [torch.full((m, n_total), float("nan"), dtype=torch.float16, device="cuda") for _ in range(blocks - 1)]
     src = (ctypes.c_void_p * len(outs))(*[mine.data_ptr() + rank * n_local * 2] * len(outs))
     dst = (ctypes.c_void_p * len(outs))(*[o.data_ptr() + rank * n_local * 2 for o in outs])
-    _lib.check(cuda_lib.nvfp4_copy_column_blocks(dst, src, len(outs), row0, rows, n_local, n_total, 3, torch.cuda.current_stream().cuda_stream))
+    _lib.check(cuda_lib.nvfp4_copy_column_blocks(dst, src, len(outs), row0, rows, n_local, n_total, 3, 1, torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()
     for o in outs:
         blk = o[row0:row0 + rows, rank * n_local:(rank + 1) * n_local]

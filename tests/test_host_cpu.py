@@ -141,3 +141,19 @@ def test_problem_cache_key_covers_strides_and_none_scales():
     v2 = torch.as_strided(store, (32, 256, 1), (512, 1, 32 * 512))
     assert v1.data_ptr() == v2.data_ptr() and S._layout_key(v1) != S._layout_key(v2)
     assert S._layout_key(None) == (0, (), ())
+
+
+@pytest.mark.parametrize("raster", [0, 1, 8, 16])
+@pytest.mark.parametrize("tiles_m,tiles_n,batches,k_tiles,workers", [(16, 28, 1, 28, 74), (32, 112, 1, 32, 74), (9, 18, 1, 28, 74),
+                                                                    (3, 5, 2, 4, 7), (1, 3, 1, 16, 148), (17, 4, 3, 2, 10), (2, 2, 1, 8, 4)])
+def test_tile_order_visits_every_output_tile_once(lib, tiles_m, tiles_n, batches, k_tiles, workers, raster):
+    import ctypes
+    tiles = tiles_m * tiles_n * batches
+    seen = set()
+    b, r, c = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    for t in range(tiles):
+        assert lib.nvfp4_plan_tile(tiles * k_tiles, workers, k_tiles, tiles_m, tiles_n, raster, t, ctypes.byref(b), ctypes.byref(r), ctypes.byref(c)) == 0
+        assert 0 <= b.value < batches and 0 <= r.value < tiles_m and 0 <= c.value < tiles_n
+        seen.add((b.value, r.value, c.value))
+    assert len(seen) == tiles
+    assert lib.nvfp4_plan_tile(tiles * k_tiles, workers, k_tiles, tiles_m, tiles_n, raster, tiles, ctypes.byref(b), ctypes.byref(r), ctypes.byref(c)) != 0

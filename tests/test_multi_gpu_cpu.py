@@ -112,3 +112,18 @@ def test_multicast_binding_is_refused():
     check_no_multicast(SimpleNamespace())                      # torch builds without the attribute
     with pytest.raises(RuntimeError, match="multicast"):
         check_no_multicast(SimpleNamespace(multicast_ptr=0x7F0000000000))
+
+
+def test_block_copy_plan_for_byte_blocks():
+    """The NVFP4 exchange moves byte matrices (packed values, scale atoms): a rank's block then
+    starts block_bytes * owner into a row, whatever n_local says."""
+    from nvfp4_gemm_b200.multi_gpu import plan_block_copies
+    world, bb = 4, 1792
+    bases = [0x1000_0000 * (r + 1) for r in range(world)]
+    for rank in range(world):
+        peers, src, dst = plan_block_copies(rank, world, 0, bases[rank], bases, "push", block_bytes=bb)
+        assert sorted(peers) == [r for r in range(world) if r != rank]
+        assert all(s == bases[rank] + rank * bb for s in src)
+        assert dst == [bases[r] + rank * bb for r in peers]
+        peers, src, dst = plan_block_copies(rank, world, 0, bases[rank], bases, "pull", block_bytes=bb)
+        assert src == [bases[r] + r * bb for r in peers] and dst == [bases[rank] + r * bb for r in peers]
