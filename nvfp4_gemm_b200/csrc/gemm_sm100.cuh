@@ -111,6 +111,10 @@ struct GemmSmem {
     static constexpr uint32_t kFixBufs = 12;  // barriers reserved for the landing slots
     static constexpr uint32_t kEpiOff = STAGES * kStageBytes;
     static constexpr uint32_t kBarOff = kEpiOff + kEpiBytes;
+    // Cluster split-K: one sender's share of the columns a CTA finalises, and whether the ring holds
+    // both the KS - 1 incoming pieces and the KS - 1 outgoing ones (then the exchange uses bulk copies).
+    static constexpr uint32_t kPieceBytes = (BN / KS) * kBM * 4;
+    static constexpr bool kBulkExchange = KS > 1 && 2u * (KS - 1) * kPieceBytes <= STAGES * kStageBytes;
     static constexpr bool kAccOverlap = (BN == 256 && KS == 1);        // see the TMEM column map above
     static constexpr uint32_t kNumAcc = (BN <= 128 || kAccOverlap) ? 2 : 1;
     static constexpr uint32_t kAccStride = kAccOverlap ? BN / 2 : BN;  // TMEM columns between the two accumulators
@@ -237,7 +241,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
             ptx::mbar_init(bar_empty + s * 8, 1);
         }
         for (uint32_t b = 0; b < S::kFixBufs; ++b)
-            ptx::mbar_init(bar_fix_full + b * 8, (KS > 1 && b == 0) ? 128 * (KS - 1) : (KS > 1 && b == 1) ? (KS - 1) : 1);
+            ptx::mbar_init(bar_fix_full + b * 8, (KS > 1 && b == 0) ? (S::kBulkExchange ? 1 : 128 * (KS - 1)) : (KS > 1 && b == 1) ? (KS - 1) : 1);
         for (int a = 0; a < 2; ++a) {
             ptx::mbar_init(bar_acc_full + a * 8, 1);
             ptx::mbar_init(bar_acc_empty + a * 8, 128 * CG);
@@ -545,35 +549,72 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
 
             if constexpr (KS > 1) {
                 constexpr int kMyCols = BN / KS;                     // columns this CTA finalises
-                constexpr uint32_t kPieceBytes = kMyCols * kBM * 4;  // one sender's columns, [col/4][128 rows][4]
+                constexpr uint32_t kPieceBytes = S::kPieceBytes;     // one sender's columns, [col/4][128 rows][4]
+                // Piece of rank r at rank q: q keeps the KS - 1 foreign pieces in rank order.
+                auto slot_of = [](int r, int q) { return r - (r > q ? 1 : 0); };
                 // The partial sums land in the operand ring, which is idle once a CTA's own MMAs
                 // are done (the accumulator is ready): every CTA tells its peers so, and nobody
                 // sends before all peers have said it.
-                const uint32_t land = smem_base;
+                const uint32_t land = smem_base;                                   // incoming pieces
                 const float* land_gen = reinterpret_cast<const float*>(smem_gen);
-                if (!cluster_waited) { ptx::cluster_wait(); cluster_waited = true; }
+                if (!cluster_waited) { ptx::cluster_wait(); cluster_waited = true; }   // peers are resident and initialised
                 if (epi_tid == 0) {
+                    if constexpr (S::kBulkExchange) ptx::mbar_expect_tx(bar_land, (KS - 1) * kPieceBytes);   // before anybody may send
                     for (int q = 0; q < KS; ++q)
                         if (q != ks_rank) ptx::mbar_arrive_cluster(bar_ready, q);
                 }
-                const bool peers_ready = ptx::mbar_wait_bounded<true>(bar_ready, 0u, abort_flag, timeout);
-                if (!ptx::named_bar_and(2, 128, peers_ready)) break;
-                // 1. send every peer the columns it finalises (peers are resident and initialised)
-                if (!cluster_waited) { ptx::cluster_wait(); cluster_waited = true; }
+                if constexpr (S::kBulkExchange) {
+                    // 1. The columns the peers finalise go TMEM -> registers -> this CTA's own shared
+                    //    memory (behind the landing area), and from there to each peer as ONE bulk
+                    //    copy through distributed shared memory that completes on the peer's landing
+                    //    barrier.  (Storing the registers straight into the peer's shared memory,
+                    //    16 bytes per thread and instruction, took about 150 cycles per warp
+                    //    instruction: 2500 cycles for 32 KB.)
+                    const uint32_t outb = smem_base + (KS - 1) * kPieceBytes;      // outgoing pieces
+                    float* outb_gen = reinterpret_cast<float*>(smem_gen + (KS - 1) * kPieceBytes);
 #pragma unroll 1
-                for (int q = 0; q < KS; ++q) {
-                    if (q == ks_rank) continue;
-                    const uint32_t dst = ptx::mapa_u32(land + ks_rank * kPieceBytes + row_in_tile * 16, q);
+                    for (int q = 0; q < KS; ++q) {
+                        if (q == ks_rank) continue;
+                        float* dst = outb_gen + slot_of(q, ks_rank) * (kPieceBytes / 4) + row_in_tile * 4;
 #pragma unroll 1
-                    for (int c0 = 0; c0 < kMyCols; c0 += 32) {
-                        uint32_t v[32];
-                        ptx::tc_ld_32cols(t_acc + q * kMyCols + c0, v);
-                        ptx::tc_wait_ld();
+                        for (int c0 = 0; c0 < kMyCols; c0 += 32) {
+                            uint32_t v[32];
+                            ptx::tc_ld_32cols(t_acc + q * kMyCols + c0, v);
+                            ptx::tc_wait_ld();
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            ptx::st_shared_cluster_v4(dst + (c0 / 4 + j) * (kBM * 16), v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                            for (int j = 0; j < 8; ++j)
+                                *reinterpret_cast<uint4*>(dst + (c0 / 4 + j) * (kBM * 4)) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        }
                     }
-                    ptx::mbar_arrive_cluster(bar_land, q);  // release: my stores above are visible to q
+                    ptx::fence_proxy_async_smem();      // these writes are read by the bulk copies (async proxy)
+                    ptx::named_bar_sync(1, 128);
+                    if (epi_tid == 0) {
+                        if (ptx::mbar_wait_bounded<true>(bar_ready, 0u, abort_flag, timeout)) {
+                            for (int q = 0; q < KS; ++q)
+                                if (q != ks_rank)
+                                    ptx::bulk_copy_to_cluster(ptx::mapa_u32(land + slot_of(ks_rank, q) * kPieceBytes, q),
+                                                              outb + slot_of(q, ks_rank) * kPieceBytes, kPieceBytes, ptx::mapa_u32(bar_land, q));
+                        }
+                    }
+                } else {
+                    const bool peers_ready = ptx::mbar_wait_bounded<true>(bar_ready, 0u, abort_flag, timeout);
+                    if (!ptx::named_bar_and(2, 128, peers_ready)) break;
+                    // 1. send every peer the columns it finalises, 16 bytes per thread and store
+#pragma unroll 1
+                    for (int q = 0; q < KS; ++q) {
+                        if (q == ks_rank) continue;
+                        const uint32_t dst = ptx::mapa_u32(land + slot_of(ks_rank, q) * kPieceBytes + row_in_tile * 16, q);
+#pragma unroll 1
+                        for (int c0 = 0; c0 < kMyCols; c0 += 32) {
+                            uint32_t v[32];
+                            ptx::tc_ld_32cols(t_acc + q * kMyCols + c0, v);
+                            ptx::tc_wait_ld();
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                ptx::st_shared_cluster_v4(dst + (c0 / 4 + j) * (kBM * 16), v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        }
+                        ptx::mbar_arrive_cluster(bar_land, q);  // release: my stores above are visible to q
+                    }
                 }
                 // 2. wait for the other CTAs' partial sums of my columns
                 const bool landed = ptx::mbar_wait_bounded<true>(bar_land, 0u, abort_flag, timeout);
@@ -593,7 +634,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
 #pragma unroll
                             for (int i = 0; i < 32; ++i) s[i] += __uint_as_float(v[i]);
                         } else {
-                            const float* src = land_gen + r * (kPieceBytes / 4) + (c0 / 4) * (kBM * 4) + row_in_tile * 4;
+                            const float* src = land_gen + slot_of(r, ks_rank) * (kPieceBytes / 4) + (c0 / 4) * (kBM * 4) + row_in_tile * 4;
 #pragma unroll
                             for (int j = 0; j < 8; ++j) {
                                 const float4 t = *reinterpret_cast<const float4*>(src + j * (kBM * 4));

@@ -182,6 +182,14 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar) : "memory");
 }
+// Bulk copy from this CTA's shared memory into another CTA's of the cluster (both addresses and
+// the size multiples of 16); the bytes are signalled on an mbarrier of the destination CTA.
+// dst and bar are shared::cluster addresses (mapa).
+__device__ __forceinline__ void bulk_copy_to_cluster(uint32_t dst_cluster, uint32_t src, uint32_t bytes, uint32_t bar_cluster) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst_cluster), "r"(src), "r"(bytes), "r"(bar_cluster) : "memory");
+}
 // 3-D tiled store shared -> global (bulk async-group completion).
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int x, int y, int z) {
     asm volatile(
