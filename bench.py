@@ -205,6 +205,7 @@ def main():
                          "auto = fused on 2 GPUs, push on more (the measured best of each)")
     ap.add_argument("--panels", type=int, default=0, help="N > 1: row panels the exchange is pipelined over (all modes but fused); 0 = the measured best")
     ap.add_argument("--copy-sms", type=int, default=-1, help="N > 1, push / pull: SMs reserved for the copy kernel (the GEMM runs on the rest); -1 = the measured best")
+    ap.add_argument("--nvfp4-out", action="store_true", help="N = 1, GEMM workloads: time the re-quantising epilogue variant (NVFP4 output) instead")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary per-config table")
     args = ap.parse_args()
@@ -238,8 +239,16 @@ def main():
     n_sets = int(min(8, max(3, -(-3 * l2_bytes // int(set_bytes)))))   # rotate over > 3x L2 of inputs
     sets = [generate_input(w["m"], w["n"], w["k"], w["l"], 1111 + i, device=dev) for i in range(n_sets)]
 
-    def step(i):
-        return S.custom_kernel(sets[i % n_sets])
+    if args.nvfp4_out:
+        # the GEMM with the re-quantising epilogue (packed e2m1 + scales instead of fp16): a variant
+        # for profiling and comparison, not the default workload
+        q_out = [S.gemm_epilogue(s[:6] + (None,), nvfp4_out=True) for s in sets]
+
+        def step(i):
+            return S.gemm_epilogue(sets[i % n_sets][:6] + (None,), nvfp4_out=True, out=q_out[i % n_sets])
+    else:
+        def step(i):
+            return S.custom_kernel(sets[i % n_sets])
 
     for i in range(args.warmup):
         step(i)
@@ -336,7 +345,7 @@ def main():
                 # its cuBLASLt submission, 22.6 us (out_cub.txt:16-18); its own kernels took 144 and 459 us
                 vs_baseline=(tflops / (flops / 22.6e-6 / 1e12)) if wl_key == "c1" else None,
                 dtype="e2m1 x ue4m3 -> f32 -> f16", data="synthetic",
-                config=dict(workload=w["name"], timing=f"CUDA events around a CUDA-graph replay of the K steps, median of 5; {n_sets} rotating input sets = {n_sets * set_bytes / 1e6:.0f} MB > L2 {l2_bytes / 1e6:.0f} MB",
+                config=dict(workload=w["name"] + (" [NVFP4 output variant]" if args.nvfp4_out else ""), timing=f"CUDA events around a CUDA-graph replay of the K steps, median of 5; {n_sets} rotating input sets = {n_sets * set_bytes / 1e6:.0f} MB > L2 {l2_bytes / 1e6:.0f} MB",
                             us_per_step=ms_per_step * 1e3, us_per_step_best_of_5=per_launch_ms[0] * 1e3, gb_per_s=gbs,
                             isolated_launch_us=isolated_us,
                             isolated_launch_timing="one launch between two CUDA events, stream synchronised before each, no graph, inputs rotating (cold L2); median of 60",
@@ -440,6 +449,14 @@ def extra_table(S, generate_input, dev, peaks, gpu_index):
         if sol:
             rec["task_sol_us_at_1500mhz"] = sol
             rec["sol_over_measured"] = sol / us
+        if key in ("c3", "c4_one_gpu"):
+            # the same GEMM with the result re-quantised to NVFP4 in the epilogue (bias / activation off)
+            q_out = [S.gemm_epilogue(s[:6] + (None,), nvfp4_out=True) for s in sets]
+            qus, _ = time_fn(lambda i: S.gemm_epilogue(sets[i % n_sets][:6] + (None,), nvfp4_out=True, out=q_out[i % n_sets]), n_sets,
+                             inner=2 if key == "c4_one_gpu" else 4)
+            rec["nvfp4_output_us"] = qus
+            rec["nvfp4_output_kernel"] = S.last_kernel()
+            del q_out
         if w["m"] <= 128 and w["n"] > 1:
             rec["isolated_launch_us"] = isolated_launch_us(lambda i: S.custom_kernel(sets[i % n_sets]), n_sets)
         if w["n"] > 1:
@@ -468,7 +485,7 @@ def extra_table(S, generate_input, dev, peaks, gpu_index):
 def default_exchange(world):
     """Measured-best exchange settings per GPU count (B200 / NVSwitch, the 8192 x 28672 x 8192 job):
     (mode, row panels, SMs given to the copy kernel)."""
-    return {2: ("fused", 4, 0), 4: ("push", 8, 16), 8: ("push", 16, 24)}.get(world, ("push", 8, 16))
+    return {2: ("fused", 4, 0), 4: ("fused", 4, 0), 8: ("push", 4, 0)}.get(world, ("push", 4, 0))
 
 
 def bench_column_parallel(args, w, rank, world, dev):

@@ -171,6 +171,24 @@ int nvfp4_copy_column_blocks(void* const* dst_blocks, const void* const* src_blo
                              int32_t n_local, int64_t row_stride, int32_t ctas, int32_t own_sms, void* stream);
 
 /*
+ * Peer pointers for the two functions above without any framework: one process per GPU, the
+ * exchange of the 64 handle bytes and the offset (a pipe, MPI, a file) is the caller's.
+ *   nvfp4_comm_export  in the process that owns `ptr` (any address inside a cudaMalloc'd
+ *                      allocation): fills handle_out[NVFP4_COMM_HANDLE_BYTES] and the offset of
+ *                      ptr inside its allocation;
+ *   nvfp4_comm_open    in another process, with its own GPU current: maps the allocation (peer
+ *                      access over NVLink is enabled as needed) and returns the address that
+ *                      corresponds to ptr; plain loads and stores only, no multicast binding;
+ *   nvfp4_comm_close   unmaps it again.
+ * Thin wrappers over CUDA IPC memory handles; an allocation can be opened once per process.
+ * No counterpart in the reference (single GPU, single process).
+ */
+#define NVFP4_COMM_HANDLE_BYTES 64
+int nvfp4_comm_export(const void* ptr, void* handle_out, int64_t* offset_out);
+int nvfp4_comm_open(const void* handle, int64_t offset, void** ptr_out);
+int nvfp4_comm_close(void* opened_ptr, int64_t offset);
+
+/*
  * Strided device-to-device copy (one cudaMemcpy2DAsync: `rows` pieces of `width_bytes`), used to
  * push a rank's column block of C into a peer GPU's row-major output with the copy engines while
  * the SMs compute the next row panel.  dst may be peer-mapped memory.  No counterpart in the

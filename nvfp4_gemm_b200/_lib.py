@@ -22,8 +22,9 @@ EXPORTED_SYMBOLS = (
     "nvfp4_shutdown", "nvfp4_last_error", "nvfp4_version", "nvfp4_plan_units", "nvfp4_gemm_static_scratch",
     "nvfp4_interleave_column_blocks", "nvfp4_permute_scales", "nvfp4_gemm_allgather", "nvfp4_quantize", "nvfp4_copy_2d", "nvfp4_copy_column_blocks",
     "nvfp4_unpermute_scales", "nvfp4_compare_scale_layouts", "nvfp4_gemv_config", "nvfp4_release_stream",
-    "nvfp4_gemm_epilogue", "nvfp4_plan_tile",
+    "nvfp4_gemm_epilogue", "nvfp4_plan_tile", "nvfp4_comm_export", "nvfp4_comm_open", "nvfp4_comm_close",
 )
+COMM_HANDLE_BYTES = 64
 
 ACT_NONE, ACT_RELU, ACT_SILU = 0, 1, 2
 OUT_FP16, OUT_NVFP4 = 0, 1
@@ -121,6 +122,12 @@ def load() -> ctypes.CDLL:
     lib.nvfp4_plan_units.argtypes = [c_int, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int),
                                      ctypes.POINTER(c_int), c_int]
     lib.nvfp4_plan_units.restype = c_int
+    lib.nvfp4_comm_export.argtypes = [c_void_p, c_void_p, ctypes.POINTER(c_int64)]
+    lib.nvfp4_comm_export.restype = c_int
+    lib.nvfp4_comm_open.argtypes = [c_void_p, c_int64, ctypes.POINTER(c_void_p)]
+    lib.nvfp4_comm_open.restype = c_int
+    lib.nvfp4_comm_close.argtypes = [c_void_p, c_int64]
+    lib.nvfp4_comm_close.restype = c_int
     lib.nvfp4_plan_tile.argtypes = [c_int] * 7 + [ctypes.POINTER(c_int)] * 3
     lib.nvfp4_plan_tile.restype = c_int
     lib.nvfp4_launch_count.argtypes = []

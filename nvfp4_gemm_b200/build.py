@@ -45,12 +45,14 @@ def needs_build() -> bool:
 def build(force: bool = False, verbose: bool = False) -> Path:
     if not force and not needs_build():
         return LIB
-    cmd = [find_nvcc(), *NVCC_FLAGS, "-o", str(LIB), str(SRC)]
+    tmp = LIB.with_suffix(".so.building")
+    cmd = [find_nvcc(), *NVCC_FLAGS, "-o", str(tmp), str(SRC)]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
         print(" ".join(cmd), file=sys.stderr)
     subprocess.check_call(cmd)
+    os.replace(tmp, LIB)       # a reader never sees a half-written library
     return LIB
 
 

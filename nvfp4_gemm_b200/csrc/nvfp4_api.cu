@@ -781,6 +781,50 @@ int nvfp4_copy_column_blocks(void* const* dst_blocks, const void* const* src_blo
     return NVFP4_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Peer pointers without torch: a rank exports the allocation that holds its output, the others
+// open it and get an address they can hand to nvfp4_gemm_allgather / nvfp4_copy_column_blocks.
+// ---------------------------------------------------------------------------------------------
+int nvfp4_comm_export(const void* ptr, void* handle_out, int64_t* offset_out) {
+    if (!ptr || !handle_out || !offset_out) return fail(NVFP4_ERR_INVALID_ARGUMENT, "ptr, handle_out and offset_out must not be NULL");
+    // the handle names the whole allocation: find its base and report where ptr lies inside it
+    using GetRangeFn = CUresult (*)(CUdeviceptr*, size_t*, CUdeviceptr);
+    static GetRangeFn get_range = nullptr;
+    if (!get_range) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        CUDA_TRY(cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &qres));
+        if (!fn || qres != cudaDriverEntryPointSuccess) return fail(NVFP4_ERR_CUDA, "cuMemGetAddressRange is not available from this driver");
+        get_range = reinterpret_cast<GetRangeFn>(fn);
+    }
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    const CUresult r = get_range(&base, &size, reinterpret_cast<CUdeviceptr>(ptr));
+    if (r != CUDA_SUCCESS) return fail(NVFP4_ERR_CUDA, "cuMemGetAddressRange failed (CUresult %d): not a device allocation?", static_cast<int>(r));
+    cudaIpcMemHandle_t h;
+    CUDA_TRY(cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base)));
+    static_assert(sizeof(h) == NVFP4_COMM_HANDLE_BYTES, "handle size");
+    std::memcpy(handle_out, &h, sizeof(h));
+    *offset_out = static_cast<int64_t>(reinterpret_cast<CUdeviceptr>(ptr) - base);
+    return NVFP4_OK;
+}
+
+int nvfp4_comm_open(const void* handle, int64_t offset, void** ptr_out) {
+    if (!handle || !ptr_out || offset < 0) return fail(NVFP4_ERR_INVALID_ARGUMENT, "handle and ptr_out must not be NULL, offset >= 0");
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, sizeof(h));
+    void* base = nullptr;
+    CUDA_TRY(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+    *ptr_out = static_cast<uint8_t*>(base) + offset;
+    return NVFP4_OK;
+}
+
+int nvfp4_comm_close(void* opened_ptr, int64_t offset) {
+    if (!opened_ptr || offset < 0) return fail(NVFP4_ERR_INVALID_ARGUMENT, "opened_ptr must not be NULL, offset >= 0");
+    CUDA_TRY(cudaIpcCloseMemHandle(static_cast<uint8_t*>(opened_ptr) - offset));
+    return NVFP4_OK;
+}
+
 int nvfp4_copy_2d(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch, int64_t width_bytes, int64_t rows, void* stream_v) {
     if (!dst || !src) return fail(NVFP4_ERR_INVALID_ARGUMENT, "dst and src must not be NULL");
     if (width_bytes < 1 || rows < 1 || dst_pitch < width_bytes || src_pitch < width_bytes)

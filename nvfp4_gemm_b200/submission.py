@@ -113,14 +113,16 @@ _ACTIVATIONS = {"none": _lib.ACT_NONE, "relu": _lib.ACT_RELU, "silu": _lib.ACT_S
 
 
 def gemm_epilogue(data: input_t, bias=None, activation: str = "none", nvfp4_out: bool = False, tile_n: int = 0, grid: int = 0,
-                  cta_group: int = 0, split_k: int = 0):
+                  cta_group: int = 0, split_k: int = 0, out=None):
     """The GEMM with the step that follows it fused into its epilogue: ``act(a @ b.T + bias)``.
 
     ``nvfp4_out=False`` writes fp16 into ``data[6]`` and returns it.  ``nvfp4_out=True`` returns
     the result re-quantised to NVFP4 as ``(packed, sf, sf_permuted)`` -- [M, N/2, L] packed e2m1,
     [M, N/16, L] e4m3 scales and the same scales in the permuted atom layout -- i.e. the ``a``,
     ``sfa`` and ``sfa_permuted`` of a following ``custom_kernel`` call whose K is this N; ``data[6]``
-    may then be None.  The reference writes fp16 only (sub_cub.py:98-104); no counterpart."""
+    may then be None; ``out`` may pass the triple a previous call returned, to be overwritten
+    instead of allocating a new one.  The reference writes fp16 only (sub_cub.py:98-104); no
+    counterpart."""
     from .inputs import FP4_DTYPE, SF_DTYPE
     lib = _lib.load()
     a, b = data[0], data[1]
@@ -137,19 +139,21 @@ def gemm_epilogue(data: input_t, bias=None, activation: str = "none", nvfp4_out:
             raise ValueError("bias must be a contiguous fp16 vector of length n")
         epi.bias = bias.data_ptr()
     epi.activation = _ACTIVATIONS[activation]
-    out = data[6]
+    if not nvfp4_out:
+        out = data[6]
     if nvfp4_out:
-        packed = torch.empty((l, m, n // 2), dtype=torch.uint8, device=dev)
-        sf = torch.empty((l, m, n // 16), dtype=torch.uint8, device=dev)
         rest_m, rest_k = (m + 127) // 128, n // 64
-        sf_perm = torch.empty((l, rest_m, rest_k, 32, 4, 4), dtype=torch.uint8, device=dev)
+        if out is None:
+            packed = torch.empty((l, m, n // 2), dtype=torch.uint8, device=dev)
+            sf = torch.empty((l, m, n // 16), dtype=torch.uint8, device=dev)
+            sf_perm = torch.empty((l, rest_m, rest_k, 32, 4, 4), dtype=torch.uint8, device=dev)
+            out = (packed.permute(1, 2, 0).view(FP4_DTYPE), sf.permute(1, 2, 0).view(SF_DTYPE),
+                   sf_perm.permute(3, 4, 1, 5, 2, 0).view(SF_DTYPE))
         epi.output = _lib.OUT_NVFP4
-        epi.out_packed, epi.out_sf, epi.out_sf_perm = packed.data_ptr(), sf.data_ptr(), sf_perm.data_ptr()
+        epi.out_packed, epi.out_sf, epi.out_sf_perm = out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr()
         epi.out_packed_row_stride, epi.out_packed_batch_stride = n // 2, m * (n // 2)
         epi.out_sf_row_stride, epi.out_sf_batch_stride = n // 16, m * (n // 16)
         epi.out_sf_perm_batch_stride = rest_m * rest_k * 512
-        out = (packed.permute(1, 2, 0).view(FP4_DTYPE), sf.permute(1, 2, 0).view(SF_DTYPE),
-               sf_perm.permute(3, 4, 1, 5, 2, 0).view(SF_DTYPE))
     cfg = GemmConfig(tile_n, 0, grid, cta_group, split_k, 0)
     stream = torch.cuda.current_stream(dev).cuda_stream
     with torch.cuda.device(dev):
