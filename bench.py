@@ -47,6 +47,11 @@ LEADERBOARD = {
     "gemv_m4096_k7168_l8": dict(m=4096, n=1, k=7168, l=8, sol_us=17.275),
     "gemv_m7168_k2048_l4": dict(m=7168, n=1, k=2048, l=4, sol_us=4.317),
 }
+# Data-movement kernels beside the path, timed on one GPU against the HBM copy peak.
+AUX_WORKLOADS = {
+    "quantize": "NVFP4 quantiser, bf16 8192 x 28672 -> packed e2m1 + plain and permuted e4m3 scales",
+    "exchange_copy": "copy kernel of the per-panel all-gather, 7 column blocks of 8192 x 3584 fp16 inside 8192 x 28672, source and destination on this GPU",
+}
 FP4_DENSE_PEAK_TFLOPS = 9000.0   # nominal dense FP4 tensor peak of one B200 (no measured FP4 figure exists)
 
 
@@ -198,7 +203,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + sorted(AUX_WORKLOADS),
+                    help="default: c1 on one GPU, c4 on several; 'quantize' and 'exchange_copy' time the data-movement kernels beside the path (one GPU)")
     ap.add_argument("--allgather", default="auto", choices=["auto", "fused", "push", "pull", "ce", "nccl"],
                     help="N > 1: how the column blocks are exchanged.  fused = peer stores in the GEMM epilogue; push / pull = "
                          "this library's copy kernel per row panel on a second stream; ce = copy engines; nccl = NCCL + re-layout; "
@@ -212,6 +218,9 @@ def main():
     args.warmup = max(args.warmup, 3)
 
     wl_key = args.workload or ("c1" if args.gpus == 1 else "c4")
+    if wl_key in AUX_WORKLOADS:
+        bench_aux(args, wl_key)
+        return
     w = WORKLOADS[wl_key]
     if args.impl == "reference":
         run_reference_arm(args, w)
@@ -366,6 +375,65 @@ def main():
         if not args.no_extra:
             line["other_configs"]["c0_cpu_128x256x256"] = cpu_config0_row()
     print(json.dumps(line), flush=True)
+
+
+def bench_aux(args, key):
+    """HBM-bound helper kernels (one GPU): achieved GB/s of algorithmic bytes against the measured copy peak."""
+    import ctypes
+    import torch
+    from nvfp4_gemm_b200 import _lib
+    lib = _lib.load()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    stream = torch.cuda.current_stream().cuda_stream
+    peaks = measured_peaks()
+    m, n = 8192, 28672
+    if key == "quantize":
+        xs = [torch.randn((m, n), device=dev, dtype=torch.bfloat16) for _ in range(2)]       # 2 x 470 MB > L2
+        packed = torch.empty((m, n // 2), dtype=torch.uint8, device=dev)
+        sf = torch.empty((m, n // 16), dtype=torch.uint8, device=dev)
+        perm = torch.empty(((m // 128) * (n // 64) * 512,), dtype=torch.uint8, device=dev)
+        byts = m * n * 2 + m * n // 2 + 2 * (m * n // 16)
+
+        def step(i):
+            x = xs[i % 2]
+            _lib.check(lib.nvfp4_quantize(x.data_ptr(), 1, packed.data_ptr(), sf.data_ptr(), perm.data_ptr(), m, n, n, n // 2, n // 16, stream))
+    else:
+        g = 8
+        nl = n // g
+        src = [torch.randn((m, n), device=dev).half() for _ in range(2)]
+        dst = [torch.empty((m, n), dtype=torch.float16, device=dev) for _ in range(2)]
+        byts = 2 * (g - 1) * m * nl * 2
+
+        def ptrs(t):
+            return (ctypes.c_void_p * (g - 1))(*[t.data_ptr() + (b + 1) * nl * 2 for b in range(g - 1)])
+        tables = [(ptrs(dst[i]), ptrs(src[i])) for i in range(2)]
+
+        def step(i):
+            d, s_ = tables[i % 2]
+            _lib.check(lib.nvfp4_copy_column_blocks(d, s_, g - 1, 0, m, nl, n, 0, 0, stream))
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    launches0 = lib.nvfp4_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    launches = lib.nvfp4_launch_count() - launches0
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+    gbs = byts / (ms * 1e-3) / 1e9
+    print(json.dumps(dict(metric="hbm_bytes_per_second", value=gbs, unit="GB/s", n_gpus=1, steps=args.steps, warmup=args.warmup, ms_per_step=ms,
+                          higher_is_better=True, scaling="weak", vs_baseline=None, dtype="u8", data="synthetic",
+                          config=dict(workload=AUX_WORKLOADS[key], timing="CUDA events around K back-to-back launches, two rotating buffer sets > L2"),
+                          roofline=dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s", frac=gbs / peaks["hbm_gbs"], traffic=None,
+                                        peak_source=peaks["source"]),
+                          gpu_launches=int(launches), clocks=clocks)), flush=True)
 
 
 def isolated_launch_us(fn, n_sets, n=60):

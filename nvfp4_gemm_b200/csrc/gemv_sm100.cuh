@@ -14,7 +14,6 @@
 namespace nvfp4 {
 
 constexpr int kGemvThreads = 128;
-constexpr int kGemvWarps = kGemvThreads / 32;
 
 struct GemvParams {
     const uint8_t* a;    // [L][M][K/2]
