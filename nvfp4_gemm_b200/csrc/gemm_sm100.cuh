@@ -714,13 +714,30 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                         store_buf = (store_buf + 1u) % S::kStagingBufs;
                     }
                 } else {
+                    // Everything the hand-back waits for goes to registers first (at most four
+                    // 32-column pieces), the accumulator is released, and only then the pieces are
+                    // converted and stored: the conversions (the re-quantising epilogue divides) must
+                    // not sit between the MMA warp and its accumulator.
+                    uint32_t held[kReleaseAfter][32];
+#pragma unroll
+                    for (int pos = 0; pos < kReleaseAfter; ++pos) ptx::tc_ld_32cols(t_acc + chunk_at(pos) * 32, held[pos]);
+                    ptx::tc_wait_ld();
+                    release_acc();
+#pragma unroll
+                    for (int pos = 0; pos < kReleaseAfter; ++pos) {
+                        if (row < p.M) {
+                            float s[32];
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(held[pos][i]);
+                            emit32(chunk_at(pos) * 32, s);
+                        }
+                    }
 #pragma unroll 1
-                    for (int pos = 0; pos < kChunks; ++pos) {
+                    for (int pos = kReleaseAfter; pos < kChunks; ++pos) {
                         const int c0 = chunk_at(pos) * 32;
                         uint32_t v[32];
                         ptx::tc_ld_32cols(t_acc + c0, v);
                         ptx::tc_wait_ld();
-                        if (pos + 1 == kReleaseAfter) release_acc();
                         if (row < p.M) {
                             float s[32];
 #pragma unroll

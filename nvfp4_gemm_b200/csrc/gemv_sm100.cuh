@@ -89,31 +89,11 @@ __device__ __forceinline__ void cvt_e4m3x4(uint32_t packed, float (&f)[4]) {
     f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
 }
 
-template <int R, int UNROLL = (R == 1) ? 4 : (R == 2 ? 2 : 1)>
-__global__ void __launch_bounds__(kGemvThreads) gemv_nvfp4_kernel(const GemvParams p) {
-    const int warp = threadIdx.x >> 5;
-    const int lane = threadIdx.x & 31;
-    const int l = blockIdx.y;
-    const int row0 = (blockIdx.x * (blockDim.x >> 5) + warp) * R;   // 1, 2 or 4 warps per CTA, each on its own rows
-    if (row0 >= p.M) return;
-
-    const uint8_t* b_ptr = p.b + l * p.b_batch_stride;
-    const uint8_t* sfb_ptr = p.sfb + l * p.sfb_batch_stride;
-    const uint8_t* a_ptr[R];
-    const uint8_t* sfa_ptr[R];
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const int row = min(row0 + r, p.M - 1);  // clamp: surplus rows recompute the last one and are not stored
-        a_ptr[r] = p.a + l * p.a_batch_stride + row * p.a_row_stride;
-        sfa_ptr[r] = p.sfa + l * p.sfa_batch_stride + row * p.sfa_row_stride;
-    }
-
-    float sum[R];
-#pragma unroll
-    for (int r = 0; r < R; ++r) sum[r] = 0.f;
-
-    const int n_chunks = p.K / 64;
-    for (int base = 0; base < n_chunks; base += 32 * UNROLL) {
+// A warp's share of R rows: chunks [chunk_begin, chunk_end) of 64 elements, partial sums in fp32.
+template <int R, int UNROLL>
+__device__ __forceinline__ void gemv_accumulate(const uint8_t* const (&a_ptr)[R], const uint8_t* const (&sfa_ptr)[R], const uint8_t* b_ptr,
+                                                const uint8_t* sfb_ptr, int chunk_begin, int chunk_end, int lane, float (&sum)[R]) {
+    for (int base = chunk_begin; base < chunk_end; base += 32 * UNROLL) {
         Chunk32 av[UNROLL][R];
         uint32_t sav[UNROLL][R];
         Chunk32 bv[UNROLL];
@@ -121,7 +101,7 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_nvfp4_kernel(const GemvPara
 #pragma unroll
         for (int i = 0; i < UNROLL; ++i) {
             const int chunk = base + i * 32 + lane;
-            if (chunk < n_chunks) {
+            if (chunk < chunk_end) {
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
                     av[i][r] = ld_stream_32B(a_ptr[r] + chunk * 32);
@@ -134,7 +114,7 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_nvfp4_kernel(const GemvPara
 #pragma unroll
         for (int i = 0; i < UNROLL; ++i) {
             const int chunk = base + i * 32 + lane;
-            if (chunk < n_chunks) {
+            if (chunk < chunk_end) {
                 float sfb_f[4];
                 cvt_e4m3x4(sbv[i], sfb_f);
                 float sfa_f[R][4];
@@ -171,6 +151,31 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_nvfp4_kernel(const GemvPara
             }
         }
     }
+}
+
+template <int R, int UNROLL = (R == 1) ? 4 : (R == 2 ? 2 : 1)>
+__global__ void __launch_bounds__(kGemvThreads) gemv_nvfp4_kernel(const GemvParams p) {
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int l = blockIdx.y;
+    const int row0 = (blockIdx.x * (blockDim.x >> 5) + warp) * R;   // 1, 2 or 4 warps per CTA, each on its own rows
+    if (row0 >= p.M) return;
+
+    const uint8_t* b_ptr = p.b + l * p.b_batch_stride;
+    const uint8_t* sfb_ptr = p.sfb + l * p.sfb_batch_stride;
+    const uint8_t* a_ptr[R];
+    const uint8_t* sfa_ptr[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int row = min(row0 + r, p.M - 1);  // clamp: surplus rows recompute the last one and are not stored
+        a_ptr[r] = p.a + l * p.a_batch_stride + row * p.a_row_stride;
+        sfa_ptr[r] = p.sfa + l * p.sfa_batch_stride + row * p.sfa_row_stride;
+    }
+
+    float sum[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) sum[r] = 0.f;
+    gemv_accumulate<R, UNROLL>(a_ptr, sfa_ptr, b_ptr, sfb_ptr, 0, p.K / 64, lane, sum);
 
 #pragma unroll
     for (int r = 0; r < R; ++r) {

@@ -601,12 +601,8 @@ int nvfp4_gemm_allgather(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, v
 
 int nvfp4_gemv(const nvfp4_problem* p, void* stream_v) { return nvfp4_gemv_config(p, 0, 0, stream_v); }
 
-int nvfp4_gemv_config(const nvfp4_problem* p, int rows_per_warp, int warps_per_cta, void* stream_v) {
+static int gemv_prepare(const nvfp4_problem* p, GemvParams* g) {
     if (int rc = validate_common(p)) return rc;
-    if (rows_per_warp != 0 && rows_per_warp != 1 && rows_per_warp != 2 && rows_per_warp != 4)
-        return fail(NVFP4_ERR_INVALID_ARGUMENT, "rows_per_warp must be 0 (auto), 1, 2 or 4");
-    if (warps_per_cta != 0 && warps_per_cta != 1 && warps_per_cta != 2 && warps_per_cta != 4)
-        return fail(NVFP4_ERR_INVALID_ARGUMENT, "warps_per_cta must be 0 (auto), 1, 2 or 4");
     if (!p->c) return fail(NVFP4_ERR_INVALID_ARGUMENT, "c must not be NULL");
     if (p->n != 1) return fail(NVFP4_ERR_INVALID_ARGUMENT, "the GEMV needs n == 1 (got %d)", p->n);
     if (!p->sfa || !p->sfb) return fail(NVFP4_ERR_INVALID_ARGUMENT, "the GEMV needs the plain scale tensors (sfa, sfb)");
@@ -618,24 +614,31 @@ int nvfp4_gemv_config(const nvfp4_problem* p, int rows_per_warp, int warps_per_c
     if (p->l > 1 && (p->a_batch_stride % 32 || p->b_batch_stride % 32 || p->sfa_batch_stride % 4 || p->sfb_batch_stride % 4))
         return fail(NVFP4_ERR_INVALID_ARGUMENT, "batch strides must keep 32-byte (a, b) / 4-byte (sfa, sfb) alignment");
     if (p->l > 65535) return fail(NVFP4_ERR_INVALID_ARGUMENT, "l must be <= 65535");
-
     DeviceCtx* c = nullptr;
     if (int rc = get_ctx(&c)) return rc;
     if (!c->sm100) return fail(NVFP4_ERR_UNSUPPORTED, "device %d is not sm_100", c->device);
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    g->a = static_cast<const uint8_t*>(p->a);
+    g->b = static_cast<const uint8_t*>(p->b);
+    g->sfa = static_cast<const uint8_t*>(p->sfa);
+    g->sfb = static_cast<const uint8_t*>(p->sfb);
+    g->c = static_cast<__half*>(p->c);
+    g->a_row_stride = p->a_row_stride; g->a_batch_stride = p->a_batch_stride;
+    g->b_batch_stride = p->b_batch_stride;
+    g->sfa_row_stride = p->sfa_row_stride; g->sfa_batch_stride = p->sfa_batch_stride;
+    g->sfb_batch_stride = p->sfb_batch_stride;
+    g->c_row_stride = p->c_row_stride; g->c_batch_stride = p->c_batch_stride;
+    g->M = p->m; g->K = p->k; g->L = p->l;
+    return NVFP4_OK;
+}
 
+int nvfp4_gemv_config(const nvfp4_problem* p, int rows_per_warp, int warps_per_cta, void* stream_v) {
+    if (rows_per_warp != 0 && rows_per_warp != 1 && rows_per_warp != 2 && rows_per_warp != 4)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "rows_per_warp must be 0 (auto), 1, 2 or 4");
+    if (warps_per_cta != 0 && warps_per_cta != 1 && warps_per_cta != 2 && warps_per_cta != 4)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "warps_per_cta must be 0 (auto), 1, 2 or 4");
     GemvParams g;
-    g.a = static_cast<const uint8_t*>(p->a);
-    g.b = static_cast<const uint8_t*>(p->b);
-    g.sfa = static_cast<const uint8_t*>(p->sfa);
-    g.sfb = static_cast<const uint8_t*>(p->sfb);
-    g.c = static_cast<__half*>(p->c);
-    g.a_row_stride = p->a_row_stride; g.a_batch_stride = p->a_batch_stride;
-    g.b_batch_stride = p->b_batch_stride;
-    g.sfa_row_stride = p->sfa_row_stride; g.sfa_batch_stride = p->sfa_batch_stride;
-    g.sfb_batch_stride = p->sfb_batch_stride;
-    g.c_row_stride = p->c_row_stride; g.c_batch_stride = p->c_batch_stride;
-    g.M = p->m; g.K = p->k; g.L = p->l;
+    if (int rc = gemv_prepare(p, &g)) return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
     // Rows per warp: short rows amortise the vector's dequantisation over four rows; long rows keep
     // more loads in flight with two, or with one when there are so few rows that two per warp
@@ -643,7 +646,9 @@ int nvfp4_gemv_config(const nvfp4_problem* p, int rows_per_warp, int warps_per_c
     // up, so the smallest CTAs even out the tail.  Measured on B200 over all nine combinations
     // (graph replay, cold inputs): 7168 x 16384 x 1: r1/w1 15.5 us, r2/w4 16.3; 7168 x 16384 x 4:
     // r2/w1 45.2, r2/w4 45.7, r1 49.9; 4096 x 7168 x 8: r2/w1 26.2, r4 27.8; 7168 x 2048 x 4:
-    // r4/w1 9.1, r2 10.1, r1 14.4.
+    // r4/w1 9.1, r2 10.1, r1 14.4.  (Splitting K over the warps of a CTA, one CTA per one or two
+    // rows, was measured as well: 14.7 us at best on 7168 x 16384 x 1 and slower than this
+    // everywhere else, so it is not kept.)
     const long long rows_total = static_cast<long long>(p->m) * p->l;
     const int r = rows_per_warp ? rows_per_warp : (p->k <= 4096) ? 4 : (rows_total <= 8192) ? 1 : 2;
     const int w = warps_per_cta ? warps_per_cta : 1;
