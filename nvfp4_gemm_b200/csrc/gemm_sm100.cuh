@@ -92,6 +92,8 @@ struct GemmParams {
 };
 
 constexpr uint32_t kFixChunkBytes = kBM * 32 * 4;  // 32 fp32 columns of a partial tile
+constexpr int kGlobalExchangeMinSplit = 4;         // cluster split-K: from this split on the partial sums travel through L2
+constexpr int kScratchSlotFloats = kBM * 256;      // one partial-tile slot of the library's scratch (128 x 256 fp32)
 
 template <int CG, int BN, int STAGES, bool TMA_STORE, int EPI_KB, int KS = 1>
 struct GemmSmem {
@@ -115,6 +117,9 @@ struct GemmSmem {
     // both the KS - 1 incoming pieces and the KS - 1 outgoing ones (then the exchange uses bulk copies).
     static constexpr uint32_t kPieceBytes = (BN / KS) * kBM * 4;
     static constexpr bool kBulkExchange = KS > 1 && 2u * (KS - 1) * kPieceBytes <= STAGES * kStageBytes;
+    // Wider splits exchange through global memory (L2) instead: distributed shared memory moves
+    // about 14 bytes per cycle and SM, a quarter of what an SM gets from L2.
+    static constexpr bool kGlobalExchange = KS >= kGlobalExchangeMinSplit;
     static constexpr bool kAccOverlap = (BN == 256 && KS == 1);        // see the TMEM column map above
     static constexpr uint32_t kNumAcc = (BN <= 128 || kAccOverlap) ? 2 : 1;
     static constexpr uint32_t kAccStride = kAccOverlap ? BN / 2 : BN;  // TMEM columns between the two accumulators
@@ -558,12 +563,39 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                 const uint32_t land = smem_base;                                   // incoming pieces
                 const float* land_gen = reinterpret_cast<const float*>(smem_gen);
                 if (!cluster_waited) { ptx::cluster_wait(); cluster_waited = true; }   // peers are resident and initialised
+                if constexpr (S::kGlobalExchange) {
+                    // The columns the peers finalise go TMEM -> registers -> this CTA's scratch slot in
+                    // global memory (one 128 KB slot per CTA: [destination][col/4][128 rows][4]); a
+                    // device-scope fence and one arrival on every peer's barrier publish them, and
+                    // each CTA then reads its columns of the peers' slots back through L2.
+                    float* my_slot = p.scratch + static_cast<long long>(blockIdx.x) * kScratchSlotFloats;
+#pragma unroll 1
+                    for (int q = 0; q < KS; ++q) {
+                        if (q == ks_rank) continue;
+                        float* dst = my_slot + slot_of(q, ks_rank) * (kPieceBytes / 4) + row_in_tile * 4;
+#pragma unroll 1
+                        for (int c0 = 0; c0 < kMyCols; c0 += 32) {
+                            uint32_t v[32];
+                            ptx::tc_ld_32cols(t_acc + q * kMyCols + c0, v);
+                            ptx::tc_wait_ld();
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                ptx::st_cg_v4(dst + (c0 / 4 + j) * (kBM * 4),
+                                              make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                          __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
+                        }
+                    }
+                    __threadfence();
+                    ptx::named_bar_sync(1, 128);
+                }
                 if (epi_tid == 0) {
-                    if constexpr (S::kBulkExchange) ptx::mbar_expect_tx(bar_land, (KS - 1) * kPieceBytes);   // before anybody may send
+                    if constexpr (S::kBulkExchange && !S::kGlobalExchange) ptx::mbar_expect_tx(bar_land, (KS - 1) * kPieceBytes);   // before anybody may send
                     for (int q = 0; q < KS; ++q)
                         if (q != ks_rank) ptx::mbar_arrive_cluster(bar_ready, q);
                 }
-                if constexpr (S::kBulkExchange) {
+                if constexpr (S::kGlobalExchange) {
+                    // (nothing to send: the arrival above told the peers that this CTA's slot is complete)
+                } else if constexpr (S::kBulkExchange) {
                     // 1. The columns the peers finalise go TMEM -> registers -> this CTA's own shared
                     //    memory (behind the landing area), and from there to each peer as ONE bulk
                     //    copy through distributed shared memory that completes on the peer's landing
@@ -617,7 +649,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                     }
                 }
                 // 2. wait for the other CTAs' partial sums of my columns
-                const bool landed = ptx::mbar_wait_bounded<true>(bar_land, 0u, abort_flag, timeout);
+                const bool landed = S::kGlobalExchange ? ptx::mbar_wait_bounded<true>(bar_ready, 0u, abort_flag, timeout)
+                                                       : ptx::mbar_wait_bounded<true>(bar_land, 0u, abort_flag, timeout);
                 if (!ptx::named_bar_and(2, 128, landed)) break;
                 // 3. sum in ascending rank order (my own term comes from TMEM) and store fp16
 #pragma unroll 1
@@ -633,6 +666,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                         if (r == ks_rank) {
 #pragma unroll
                             for (int i = 0; i < 32; ++i) s[i] += __uint_as_float(v[i]);
+                        } else if constexpr (S::kGlobalExchange) {
+                            const float* src = p.scratch + static_cast<long long>(blockIdx.x - ks_rank + r) * kScratchSlotFloats +
+                                               slot_of(ks_rank, r) * (kPieceBytes / 4) + (c0 / 4) * (kBM * 4) + row_in_tile * 4;
+                            float4 t[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) t[j] = ptx::ld_cg_v4(src + j * (kBM * 4));
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                s[4 * j] += t[j].x; s[4 * j + 1] += t[j].y; s[4 * j + 2] += t[j].z; s[4 * j + 3] += t[j].w;
+                            }
                         } else {
                             const float* src = land_gen + slot_of(r, ks_rank) * (kPieceBytes / 4) + (c0 / 4) * (kBM * 4) + row_in_tile * 4;
 #pragma unroll

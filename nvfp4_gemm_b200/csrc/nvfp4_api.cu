@@ -325,6 +325,9 @@ int launch_gemm_splitk(DeviceCtx* c, int variant, GemmParams& params, cudaStream
     cfg.attrs = attr;
     cfg.numAttrs = 2;
     const int tiles = params.total_units / params.k_tiles;
+    if (S::kGlobalExchange && tiles * KS > 2 * kMaxCtas)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "split_k = %d over %d tiles needs %d scratch slots, the library keeps %d: use split_k 1 or 2",
+                    KS, tiles, tiles * KS, 2 * kMaxCtas);
     cfg.gridDim = dim3(tiles * KS, 1, 1);
     CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, params));
     g_launches.fetch_add(1);
@@ -519,9 +522,10 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, const nvfp4_
         ks = 1;
         const long long tiles128 = static_cast<long long>(p->n / 128) * p->l;
         if (p->m <= kBM && cf.cta_group != 2 && cf.tile_n == 0 && cf.grid == 0) {
-            // measured: two CTAs per tile beat four whenever both fit in one wave (the exchange
-            // grows with the cluster); four only pays when there are very few tiles
-            if (tiles128 * 4 <= c->num_sms / 2 && g.k_tiles >= 16 && !epi) ks = 4;
+            // measured (four exchanges its partial sums through L2, two through distributed shared
+            // memory): four CTAs per tile win when they fit one wave (128 x 4096 x 7168: 10.1 vs
+            // 10.6 us), two otherwise (128 x 7168 x 16384: 17.5 us; 4 x 256-wide 20.3)
+            if (tiles128 * 4 <= c->num_sms && g.k_tiles >= 16 && !epi) ks = 4;
             else if (tiles128 * 2 <= c->num_sms && g.k_tiles >= 16) ks = 2;   // shorter K: one whole tile per CTA wins
         }
     }

@@ -322,6 +322,11 @@ __host__ __device__ constexpr uint32_t idesc_nvf4(int mma_m, int mma_n) {
 }
 
 // ------------------------------------------------------------ global memory
+__device__ __forceinline__ float4 ld_cg_v4(const float* addr) {
+    float4 v;
+    asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(addr) : "memory");
+    return v;
+}
 __device__ __forceinline__ void st_cg_v4(float* addr, float4 v) {
     asm volatile("st.global.cg.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
