@@ -526,7 +526,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                         for (int h = 0; h < 2; ++h) {
                             float v[16];
 #pragma unroll
-                            for (int i = 0; i < 16; ++i) v[i] = __half2float(__float2half_rn(s[16 * h + i]));
+                            for (int i = 0; i < 8; ++i) {   // round to fp16 and back, two at a time
+                                const float2 f = __half22float2(__floats2half2_rn(s[16 * h + 2 * i], s[16 * h + 2 * i + 1]));
+                                v[2 * i] = f.x;
+                                v[2 * i + 1] = f.y;
+                            }
                             uint32_t o[2];
                             sf[h] = quantize_block16(v, o);
                             q[2 * h] = o[0];

@@ -10,6 +10,30 @@ namespace nvfp4 {
 // One 16-element block -> eight bytes of e2m1 codes (out[0], out[1]; low nibble = lower index) and
 // the block's e4m3 scale byte: scale = RN-even saturating e4m3 of max|v| / 6, element =
 // RN-even saturating e2m1 of v / scale (all zero when the scale is zero).
+//
+// The inputs must be fp16- or bf16-representable (both callers convert from those types).  Then
+// v / scale need not be an IEEE division: q = v * r corrected once by the exact residual
+// (v - q * scale) * r, with r within two ulp of 1 / scale, lands exactly on every e2m1 rounding
+// threshold that the true quotient hits, and everywhere else the quotient is at least 2^-11 away
+// (relatively) from a threshold because v has at most 11 significant bits and threshold * scale at
+// most 7.  Checked exhaustively on the CPU over every fp16 and bf16 value and every e4m3 scale.
+// Values beyond +-65504 (bf16 inputs, infinities) are clamped there first: the scale is then 448 and
+// the element saturates either way, while an infinity would poison the residual.
+// Eight bytes of e2m1 codes of v[0..15] / scale, scale > 0 an e4m3 value and |v| <= 65504.
+__device__ __forceinline__ void encode_block16(const float (&v)[16], float scale, uint32_t (&out)[2]) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(scale));
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        float a = v[2 * j] * r, b = v[2 * j + 1] * r;
+        a = copysignf(fmaf(fmaf(-a, scale, v[2 * j]), r, a), v[2 * j]);   // the sign only differs for -0 (its residual is +0)
+        b = copysignf(fmaf(fmaf(-b, scale, v[2 * j + 1]), r, b), v[2 * j + 1]);
+        uint32_t byte;
+        asm("{\n\t.reg .b8 q;\n\tcvt.rn.satfinite.e2m1x2.f32 q, %1, %2;\n\tcvt.u32.u8 %0, q;\n\t}" : "=r"(byte) : "f"(b), "f"(a));
+        out[j >> 2] |= byte << (8 * (j & 3));
+    }
+}
+
 __device__ __forceinline__ uint8_t quantize_block16(const float (&v)[16], uint32_t (&out)[2]) {
     float amax = 0.f;
 #pragma unroll
@@ -23,12 +47,13 @@ __device__ __forceinline__ uint8_t quantize_block16(const float (&v)[16], uint32
     out[0] = 0u;
     out[1] = 0u;
     if (scale > 0.f) {
+        if (amax <= 65504.f) {
+            encode_block16(v, scale, out);
+        } else {
+            float w[16];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const float a = __fdiv_rn(v[2 * j], scale), b = __fdiv_rn(v[2 * j + 1], scale);
-            uint32_t byte;
-            asm("{\n\t.reg .b8 q;\n\tcvt.rn.satfinite.e2m1x2.f32 q, %1, %2;\n\tcvt.u32.u8 %0, q;\n\t}" : "=r"(byte) : "f"(b), "f"(a));
-            out[j >> 2] |= byte << (8 * (j & 3));
+            for (int j = 0; j < 16; ++j) w[j] = fminf(fmaxf(v[j], -65504.f), 65504.f);
+            encode_block16(w, scale, out);
         }
     }
     return static_cast<uint8_t>(sf_pair & 0xff);

@@ -32,12 +32,62 @@ def test_quantizer_matches_oracle_bit_for_bit(cuda_lib, oracle, dtype, rows, k):
     g = torch.Generator().manual_seed(rows + k)
     x = (torch.randn((rows, k), generator=g) * torch.exp(torch.randn((rows, 1), generator=g))).to(dtype)
     x[0, :16] = 0                                   # an all-zero block
+    x[-1, 20] = -0.0                                # a negative zero keeps its sign bit in the code
     x[-1, -16:] = 1000.0 if dtype == torch.float16 else 1e6   # saturating scale / elements
     packed, sf, perm = _quantize(cuda_lib, x.cuda())
     exp_packed, exp_sf = oracle.quantize_rows(x.float().numpy())
     assert np.array_equal(sf.cpu().numpy(), exp_sf)
     assert np.array_equal(packed.cpu().numpy(), exp_packed)
     assert np.array_equal(perm.cpu().numpy(), oracle.permute_sf(exp_sf[:, :, None]))
+
+
+def _e4m3_positive():
+    vals = []
+    for byte in range(1, 127):
+        e, m = (byte >> 3) & 15, byte & 7
+        vals.append((m / 8) * 2.0 ** -6 if e == 0 else (1 + m / 8) * 2.0 ** (e - 7))
+    return np.array(vals, dtype=np.float32)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_quantizer_on_rounding_ties_and_their_neighbours(cuda_lib, oracle, dtype):
+    """Every e4m3 scale, with elements on each e2m1 rounding threshold times the scale and one step of
+    the input type either side: the cases a division that is not correctly rounded would get wrong."""
+    scales = _e4m3_positive()
+    ties = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], dtype=np.float32)
+    rows = []
+    for s in scales:
+        on = torch.tensor(ties * s).to(dtype)
+        if not torch.isfinite(on.float()).all():
+            continue
+        bits = on.view(torch.int16)
+        block = torch.cat([on, (bits + 1).view(dtype), (bits - 1).view(dtype)])         # 21 values
+        signs = torch.tensor([1.0, -1.0] * 11)[:21].to(dtype)
+        for part in (block[:15], block[6:21]):
+            row = torch.zeros(64, dtype=dtype)
+            row[:15] = part * signs[:15]
+            row[15] = 6.0 * float(s)                                                    # pins the block's scale to s
+            row[16:31] = part
+            row[31] = -6.0 * float(s)
+            rows.append(row)
+    x = torch.stack(rows)
+    assert torch.isfinite(x.float()).all()
+    packed, sf, _ = _quantize(cuda_lib, x.cuda())
+    exp_packed, exp_sf = oracle.quantize_rows(x.float().numpy())
+    assert np.array_equal(sf.cpu().numpy(), exp_sf)
+    assert np.array_equal(packed.cpu().numpy(), exp_packed)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_quantizer_saturates_infinities_and_huge_values(cuda_lib, oracle, dtype):
+    x = torch.zeros((2, 64), dtype=dtype)
+    x[0, 0], x[0, 1], x[0, 2], x[0, 3] = float("inf"), float("-inf"), 3.0, 60000.0
+    x[0, 18], x[0, 19], x[0, 20] = 448.0 * 5, 448.0 * 5.5, 65504.0 if dtype == torch.float16 else 3e38
+    x[1, 5], x[1, 6] = (65504.0, -1.0) if dtype == torch.float16 else (-1e30, 1e20)
+    packed, sf, _ = _quantize(cuda_lib, x.cuda())
+    exp_packed, exp_sf = oracle.quantize_rows(x.float().numpy())
+    assert np.array_equal(sf.cpu().numpy(), exp_sf)
+    assert np.array_equal(packed.cpu().numpy(), exp_packed)
 
 
 def test_quantize_then_gemm_approximates_the_fp32_product(cuda_lib, oracle):
