@@ -307,6 +307,16 @@ int nvfp4_selftest_bounded_wait(void* stream);
 int nvfp4_plan_units(int total_units, int grid, int cta, int* begin, int* end, int* first_tile_slot, int k_tiles);
 
 /*
+ * The order in which a persistent worker walks its range: segment `index` (0, 1, ...) as a
+ * half-open unit range inside ONE output tile, or begin = end = -1 past the last one.  Order: the
+ * partial tile the range starts in, the whole tiles but the last, the partial tile the range ends
+ * in, the last whole tile.  A tile shared by two workers is finished by the one holding the start
+ * of its k-range (its last-but-one segment); the other one published its partial sums in its
+ * first segment, and the summing runs beside the MMAs of the finisher's last whole tile.
+ */
+int nvfp4_plan_segment(int total_units, int grid, int cta, int k_tiles, int index, int* begin, int* end);
+
+/*
  * Host-side view of the persistent GEMM's tile order (no GPU needed): which output tile (batch,
  * row tile, column tile) the `tile`-th entry of the workers' linear tile sequence is.  The order
  * is chosen so that the tiles the workers process at the same time are neighbours in the output

@@ -91,7 +91,6 @@ struct GemmParams {
     int total_units;                // tiles_m * tiles_n * L * k_tiles
 };
 
-constexpr uint32_t kFixChunkBytes = kBM * 32 * 4;  // 32 fp32 columns of a partial tile
 constexpr int kGlobalExchangeMinSplit = 4;         // cluster split-K: from this split on the partial sums travel through L2
 constexpr int kScratchSlotFloats = kBM * 256;      // one partial-tile slot of the library's scratch (128 x 256 fp32)
 
@@ -108,9 +107,7 @@ struct GemmSmem {
     static constexpr uint32_t kEpiBytes = EPI_KB * 1024;
     static constexpr uint32_t kStagingBufs = TMA_STORE ? (EPI_KB * 1024 / 4) / 4096 : 2;   // 32-row x 128-byte buffers per epilogue warp
     static constexpr uint32_t kStagingPerWarp = kStagingBufs * 32 * 128;
-    // The finisher of a shared tile lands other workers' partials in the (then idle) operand ring.
-    static constexpr uint32_t kFixSlots = (STAGES * kStageBytes / kFixChunkBytes) < 12 ? (STAGES * kStageBytes / kFixChunkBytes) : 12;
-    static constexpr uint32_t kFixBufs = 12;  // barriers reserved for the landing slots
+    static constexpr uint32_t kFixBufs = 2;   // barriers of the cluster split-K exchange ("landed", "ready")
     static constexpr uint32_t kEpiOff = STAGES * kStageBytes;
     static constexpr uint32_t kBarOff = kEpiOff + kEpiBytes;
     // Cluster split-K: one sender's share of the columns a CTA finalises, and whether the ring holds
@@ -123,13 +120,12 @@ struct GemmSmem {
     static constexpr bool kAccOverlap = (BN == 256 && KS == 1);        // see the TMEM column map above
     static constexpr uint32_t kNumAcc = (BN <= 128 || kAccOverlap) ? 2 : 1;
     static constexpr uint32_t kAccStride = kAccOverlap ? BN / 2 : BN;  // TMEM columns between the two accumulators
-    // full[STAGES] empty[STAGES] acc_full[2] acc_empty[2] fix_full[kFixBufs] | tmem slot | abort | finisher
+    // full[STAGES] empty[STAGES] acc_full[2] acc_empty[2] exchange[kFixBufs] | tmem slot | abort
     static constexpr uint32_t kNumBars = 2 * STAGES + 4 + kFixBufs;
     static constexpr uint32_t kBytes = kBarOff + kNumBars * 8 + 16;
     static constexpr uint32_t kDynamicBytes = kBytes + 1024;  // slack for manual 1024-byte alignment
     static_assert(kStageBytes % 1024 == 0, "stage tiles must keep 1024-byte alignment");
     static_assert(!TMA_STORE || kEpiBytes >= 4 * kStagingPerWarp, "TMA-store staging does not fit");
-    static_assert(kFixSlots >= 2, "the partial-tile reduction needs at least two landing slots");
     static_assert(KS == 1 || (CG == 1 && BN / KS >= 32 && STAGES * kStageBytes >= kBM * BN * 4),
                   "cluster split-K: single-CTA MMAs, at least 32 columns per CTA, the ring must hold one fp32 tile");
     static_assert(kDynamicBytes <= 232448, "exceeds the 227 KB of shared memory one CTA may use");
@@ -147,6 +143,45 @@ __host__ __device__ inline int unit_owner(int u, int n, int total_units) {
     while (c > 0 && unit_boundary(c, n, total_units) > u) --c;
     return c;
 }
+// The i-th piece of work ("segment": consecutive k-tiles of ONE output tile) of a worker whose
+// unit range is [ub, ue): the partial tile the range starts in, the whole tiles but the last, the
+// partial tile the range ends in, the last whole tile.  A tile shared by two workers is finished
+// by the one that holds the start of its k-range, i.e. in that worker's last-but-one segment:
+// the other worker published its partial sums in its very first segment, long before, and the
+// summing runs beside the MMAs of the finisher's last whole tile, so that nothing but an
+// ordinary epilogue follows a worker's last MMA.  False when i is past the end.
+struct Segment {
+    int u0, u1, tile;
+};
+struct SegmentPlan {
+    int ub, ue, head_end, tail_begin, n_head, n_tail, whole, k_tiles, first_tile, last_tile;
+    // (two independent divisions: this runs in front of every role's first instruction)
+    __host__ __device__ SegmentPlan(int ub_, int ue_, int k_tiles_) : ub(ub_), ue(ue_), k_tiles(k_tiles_) {
+        first_tile = ub / k_tiles;                              // tile the range starts in
+        last_tile = ue / k_tiles;                               // tile the range ends in (or just before)
+        n_head = ub != first_tile * k_tiles ? 1 : 0;
+        head_end = (first_tile + n_head) * k_tiles;             // first tile boundary at or after ub
+        if (head_end > ue) head_end = ue;
+        tail_begin = last_tile * k_tiles;                       // last tile boundary at or before ue
+        if (tail_begin < head_end) tail_begin = head_end;
+        n_tail = ue > tail_begin ? 1 : 0;
+        whole = last_tile - (first_tile + n_head);
+        if (whole < 0) whole = 0;
+    }
+    __host__ __device__ bool at(int i, Segment* out) const {
+        if (i < n_head) { *out = Segment{ub, head_end, first_tile}; return true; }
+        int j = i - n_head;                                     // position among [whole..., tail, last whole]
+        if (j >= whole + n_tail) return false;
+        if (n_tail) {
+            const int tail_pos = whole > 0 ? whole - 1 : 0;
+            if (j == tail_pos) { *out = Segment{tail_begin, ue, last_tile}; return true; }
+            if (j > tail_pos) --j;
+        }
+        *out = Segment{head_end + j * k_tiles, head_end + (j + 1) * k_tiles, first_tile + n_head + j};
+        return true;
+    }
+};
+
 // Where tile `tile` of the workers' linear tile sequence lies in the output: (batch, row tile,
 // column tile).  Worker w walks the contiguous tile indices of its unit range, so at any moment
 // the workers sit at the same RELATIVE position r in their ranges.  Tiles are therefore ranked by
@@ -279,6 +314,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
         ptx::tmem_relinquish<CG>();
         ptx::tc_fence_before();
     }
+    // This CTA's share of the work, worked out before the wait below: it reads kernel parameters only.
+    const int KT = p.k_tiles;
+    const int n_workers = (KS > 1) ? static_cast<int>(gridDim.x) : static_cast<int>(gridDim.x) / CG;
+    const int worker = (KS > 1) ? static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x) / CG;
+    // stream-K: equal share of all units.  Cluster split-K: tile = cluster index, k-range by rank.
+    const int u_begin = (KS > 1) ? (worker / KS) * KT + (ks_rank * KT) / KS : unit_boundary(worker, n_workers, p.total_units);
+    const int u_end = (KS > 1) ? (worker / KS) * KT + ((ks_rank + 1) * KT) / KS : unit_boundary(worker + 1, n_workers, p.total_units);
+    const uint64_t timeout = p.timeout_cycles;
+    const SegmentPlan plan(u_begin, u_end, KT);   // (a cluster split-K CTA has one segment: its share of the tile's k-range)
+    Segment first_seg{0, 0, 0};
+    plan.at(0, &first_seg);
+    const TileCoord first_tc = tile_coords(first_seg.tile, n_workers, KT, p.total_units, p.tiles_m, p.tiles_n, (KS > 1) ? 0 : p.raster_rows);
     // Kernels of this library are often launched back to back (a decode step is a chain of short
     // GEMMs): let the next launch's CTAs set up (barriers, TMEM, descriptor prefetch) on SMs this
     // grid leaves idle or frees, and touch global memory only after everything the stream ordered
@@ -291,13 +338,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
         tmem_base = *tmem_slot_gen;
     }
 
-    const int KT = p.k_tiles;
-    const int n_workers = (KS > 1) ? static_cast<int>(gridDim.x) : static_cast<int>(gridDim.x) / CG;
-    const int worker = (KS > 1) ? static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x) / CG;
-    // stream-K: equal share of all units.  Cluster split-K: tile = cluster index, k-range by rank.
-    const int u_begin = (KS > 1) ? (worker / KS) * KT + (ks_rank * KT) / KS : unit_boundary(worker, n_workers, p.total_units);
-    const int u_end = (KS > 1) ? (worker / KS) * KT + ((ks_rank + 1) * KT) / KS : unit_boundary(worker + 1, n_workers, p.total_units);
-    const uint64_t timeout = p.timeout_cycles;
 
     // Warps 0 and 1 run their loops with all 32 lanes converged and hand the single-thread
     // instructions (TMA, tcgen05) to one lane chosen by elect.sync: the compiler then knows the
@@ -308,13 +348,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
         // A is re-read by every n-tile (keep it in L2); B streams through once per m-tile.
         const uint64_t pol_a = ptx::policy_evict_last();
         const uint64_t pol_b = (p.tiles_m * CG <= 2) ? ptx::policy_evict_first() : ptx::policy_evict_last();
+        // The scales are re-read like the operands they belong to.  With few row tiles (decode) B and
+        // its scales stream through once and the hint only costs: those loads go without one.
+        const bool hint_sf = p.tiles_m * CG > 2;
         uint32_t stage = 0, phase = 0;
         bool ok = true;
-        for (int u = u_begin; u < u_end && ok;) {
-            const int tile = u / KT;
-            const int k0 = u - tile * KT;
-            const int k1 = min(KT, k0 + (u_end - u));
-            const TileCoord tc = tile_coords(tile, n_workers, KT, p.total_units, p.tiles_m, p.tiles_n, (KS > 1) ? 0 : p.raster_rows);
+        Segment seg;
+        for (int si = 0; ok && plan.at(si, &seg); ++si) {
+            const int tile = seg.tile;
+            const int k0 = seg.u0 - tile * KT;
+            const int k1 = k0 + (seg.u1 - seg.u0);
+            const TileCoord tc = (si == 0) ? first_tc : tile_coords(tile, n_workers, KT, p.total_units, p.tiles_m, p.tiles_n, (KS > 1) ? 0 : p.raster_rows);
             const int nb = tc.nt;
             const int mb = tc.mt * CG + cta_rank;  // 128-row block of this CTA
             const int l = tc.l;
@@ -334,8 +378,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                         ptx::mbar_expect_tx(full, S::kStageBytes);
                         ptx::tma_load_3d(sa, &p.tma_a, kt * kBKBytes, mb * kBM, l, full, pol_a);
                         ptx::tma_load_3d(sb, &p.tma_b, kt * kBKBytes, nb * BN, l, full, pol_b);
-                        ptx::tma_load_4d(ssfa, &p.tma_sfa, 0, kt * kMmaPerStage, mb, l, full);
-                        ptx::tma_load_4d(ssfb, &p.tma_sfb, 0, kt * kMmaPerStage, nb * (BN / 128), l, full);
+                        if (hint_sf) {
+                            ptx::tma_load_4d(ssfa, &p.tma_sfa, 0, kt * kMmaPerStage, mb, l, full, pol_a);
+                            ptx::tma_load_4d(ssfb, &p.tma_sfb, 0, kt * kMmaPerStage, nb * (BN / 128), l, full, pol_b);
+                        } else {
+                            ptx::tma_load_4d(ssfa, &p.tma_sfa, 0, kt * kMmaPerStage, mb, l, full);
+                            ptx::tma_load_4d(ssfb, &p.tma_sfb, 0, kt * kMmaPerStage, nb * (BN / 128), l, full);
+                        }
                     } else {
                         // Both CTAs of the pair report to the leader's barrier, which expects the
                         // bytes of both stages (a completion may precede the expectation: the
@@ -344,14 +393,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                         if (leader) ptx::mbar_expect_tx(bar_full + stage * 8, 2 * S::kStageBytes);
                         ptx::tma_load_3d_pair(sa, &p.tma_a, kt * kBKBytes, mb * kBM, l, full, pol_a);
                         ptx::tma_load_3d_pair(sb, &p.tma_b, kt * kBKBytes, nb * BN + cta_rank * kBRows, l, full, pol_b);
-                        ptx::tma_load_4d_pair(ssfa, &p.tma_sfa, 0, kt * kMmaPerStage, mb, l, full);
-                        ptx::tma_load_4d_pair(ssfb, &p.tma_sfb, 0, kt * kMmaPerStage, nb * (BN / 128), l, full);
+                        if (hint_sf) {
+                            ptx::tma_load_4d_pair(ssfa, &p.tma_sfa, 0, kt * kMmaPerStage, mb, l, full, pol_a);
+                            ptx::tma_load_4d_pair(ssfb, &p.tma_sfb, 0, kt * kMmaPerStage, nb * (BN / 128), l, full, pol_b);
+                        } else {
+                            ptx::tma_load_4d_pair(ssfa, &p.tma_sfa, 0, kt * kMmaPerStage, mb, l, full);
+                            ptx::tma_load_4d_pair(ssfb, &p.tma_sfb, 0, kt * kMmaPerStage, nb * (BN / 128), l, full);
+                        }
                     }
                 }
                 __syncwarp();
                 if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
-            u += k1 - k0;
         }
     } else if (warp == 1) {
         if (leader) {
@@ -359,10 +412,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
             constexpr uint32_t idesc = ptx::idesc_nvf4(kBM * CG, BN);
             uint32_t stage = 0, phase = 0, acc_it = 0, sf_it = 0;
             bool ok = true;
-            for (int u = u_begin; u < u_end && ok;) {
-                const int tile = u / KT;
-                const int k0 = u - tile * KT;
-                const int k1 = min(KT, k0 + (u_end - u));
+            Segment seg;
+            for (int si = 0; ok && plan.at(si, &seg); ++si) {
+                const int k0 = seg.u0 - seg.tile * KT;
+                const int k1 = k0 + (seg.u1 - seg.u0);
                 const uint32_t acc = acc_it % kNumAcc;
                 // Overlapped accumulators: one hand-back per tile on barrier 0 (the previous tile's
                 // shared half is drained; the tile before that, in this accumulator, was drained
@@ -444,7 +497,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                     kt += group;
                 }
                 ++acc_it;
-                u += k1 - k0;
             }
         }
         // (the second CTA of a pair has nothing to issue: the leader's instructions drive both)
@@ -455,12 +507,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
         const int epi_tid = threadIdx.x - 64;  // 0..127
         uint32_t acc_it = 0;
         uint32_t store_buf = 0;
-        uint32_t fix_parity = 0;  // phase parity of each landing-slot barrier
-        for (int u = u_begin; u < u_end;) {
-            const int tile = u / KT;
-            const int k0 = u - tile * KT;
-            const int k1 = min(KT, k0 + (u_end - u));
-            const TileCoord tc = tile_coords(tile, n_workers, KT, p.total_units, p.tiles_m, p.tiles_n, (KS > 1) ? 0 : p.raster_rows);
+        Segment seg;
+        for (int si = 0; plan.at(si, &seg); ++si) {
+            const int tile = seg.tile;
+            const int k0 = seg.u0 - tile * KT;
+            const int k1 = k0 + (seg.u1 - seg.u0);
+            const TileCoord tc = (si == 0) ? first_tc : tile_coords(tile, n_workers, KT, p.total_units, p.tiles_m, p.tiles_n, (KS > 1) ? 0 : p.raster_rows);
             const int nb = tc.nt;
             const int mb = tc.mt * CG + cta_rank;
             const int l = tc.l;
@@ -795,38 +847,61 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                 }
             } else {
                 // Tile shared with other workers.  Whoever holds the START of the tile's k-range
-                // (its last piece of work: the tile continues in the next workers' ranges, which
-                // they process first) finishes the tile; everyone else publishes an fp32 partial.
+                // finishes the tile; everyone else publishes an fp32 partial.  The others hold the
+                // tile at the start of their ranges and contract it first of all, the finisher holds
+                // it at the end of its range and contracts it last but one.
                 const int w_first = unit_owner(tile * KT, n_workers, p.total_units);
                 int* counter = p.counters + w_first * CG + cta_rank;
                 if (k0 > 0) {
                     // Publish.  Slot layout [BN/4][128 rows][4] keeps every warp-wide 16-byte access
-                    // contiguous (512 bytes) and a 32-column chunk contiguous (16 KB).
+                    // contiguous (512 bytes) and a 32-column chunk contiguous (16 KB).  What the
+                    // hand-back waits for goes to registers first.
                     float* my_slot = p.scratch + static_cast<long long>(partial_slot(worker, k0, CG, cta_rank)) * (kBM * BN);
-#pragma unroll 1
-                    for (int pos = 0; pos < kChunks; ++pos) {
-                        const int c0 = chunk_at(pos) * 32;
-                        uint32_t v[32];
-                        ptx::tc_ld_32cols(t_acc + c0, v);
-                        ptx::tc_wait_ld();
-                        if (pos + 1 == kReleaseAfter) release_acc();  // the MMA warp may start the next tile now
+                    auto publish32 = [&](int c0, const uint32_t (&v)[32]) {
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
                             ptx::st_cg_v4(my_slot + ((c0 / 4 + j) * kBM + row_in_tile) * 4,
                                           make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
                                                       __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
+                    };
+                    if constexpr (kAccOverlap) {
+                        uint32_t held[kReleaseAfter][32];
+#pragma unroll
+                        for (int pos = 0; pos < kReleaseAfter; ++pos) ptx::tc_ld_32cols(t_acc + chunk_at(pos) * 32, held[pos]);
+                        ptx::tc_wait_ld();
+                        release_acc();  // the MMA warp may start the next tile now
+#pragma unroll
+                        for (int pos = 0; pos < kReleaseAfter; ++pos) publish32(chunk_at(pos) * 32, held[pos]);
                     }
+#pragma unroll 1
+                    for (int pos = kAccOverlap ? kReleaseAfter : 0; pos < kChunks; ++pos) {
+                        const int c0 = chunk_at(pos) * 32;
+                        uint32_t v[32];
+                        ptx::tc_ld_32cols(t_acc + c0, v);
+                        ptx::tc_wait_ld();
+                        publish32(c0, v);
+                    }
+                    if constexpr (!kAccOverlap) release_acc();
                     __threadfence();
                     ptx::named_bar_sync(1, 128);
                     if (epi_tid == 0) atomicAdd(counter, k1 - k0);
                 } else {
-                    // Finish: wait until the rest of the k-range has been published (normally long
-                    // ago), pull those partials into the now idle operand ring with bulk copies --
-                    // as many 16 KB chunks in flight as the ring holds -- and add them to this
-                    // worker's accumulator in ascending worker order.
+                    // Finish: the rest of the k-range has been published (normally long ago); add
+                    // those partials, read straight from L2, to this worker's accumulator in
+                    // ascending worker order.  The operand ring keeps this SM's path from L2 busy,
+                    // so a load issued here comes back after a microsecond or more: 64 columns of a
+                    // contributor (64 registers) are requested before anything is added.
                     const int w_last = unit_owner(tile * KT + KT - 1, n_workers, p.total_units);
-                    const int n_others = w_last - w_first;
                     const int need = KT - (k1 - k0);
+                    // The half an overlapped accumulator shares with the other one goes to registers
+                    // and is handed back before anything is waited for: the MMA warp moves on.
+                    uint32_t held[kAccOverlap ? kReleaseAfter : 1][32];
+                    if constexpr (kAccOverlap) {
+#pragma unroll
+                        for (int pos = 0; pos < kReleaseAfter; ++pos) ptx::tc_ld_32cols(t_acc + chunk_at(pos) * 32, held[pos]);
+                        ptx::tc_wait_ld();
+                        release_acc();
+                    }
                     bool ready = true;
                     if (epi_tid == 0) {
                         const long long t_spin = clock64();
@@ -838,60 +913,55 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                             }
                             __nanosleep(64);
                         }
-                        ptx::fence_proxy_async_all();  // other CTAs' plain stores -> this CTA's bulk reads
-                    }
-                    if constexpr (TMA_STORE) {
-                        if (lane == 0) ptx::bulk_wait_group<0>();  // earlier tile stores of this warp have left shared memory
                     }
                     if (!ptx::named_bar_and(1, 128, ready)) break;
-                    constexpr int kChunksPerTile = BN / 32;
-                    constexpr int kSlots = S::kFixSlots;
-                    const int n_chunks = kChunksPerTile * n_others;          // chunk q = (column chunk, contributor)
-                    const float* land_gen = reinterpret_cast<const float*>(smem_gen);
-                    auto issue = [&](int q) {
-                        const int ci = q / n_others, wi = q - ci * n_others;
-                        const int slot = ((w_first + 1 + wi) * 2) * CG + cta_rank;   // later contributors use their "head" slot
-                        const float* src = p.scratch + static_cast<long long>(slot) * (kBM * BN) + static_cast<long long>(ci) * (kFixChunkBytes / 4);
-                        const int b = q % kSlots;
-                        ptx::mbar_expect_tx(bar_fix_full + b * 8, kFixChunkBytes);
-                        ptx::bulk_load(smem_base + b * kFixChunkBytes, src, kFixChunkBytes, bar_fix_full + b * 8);
-                    };
-                    if (epi_tid == 0)
-                        for (int q = 0; q < n_chunks && q < kSlots; ++q) issue(q);
-                    bool fix_ok = true;
+                    static_assert(kChunks % 2 == 0, "the partial sums are added 64 columns at a time");
+                    // the columns [c0a, c0a + 32) and [c0b, c0b + 32) of this thread's row: own sums in, total out
+                    auto add_others_and_emit = [&](int c0a, int c0b, float (&sa)[32], float (&sb)[32]) {
 #pragma unroll 1
-                    for (int ci = 0; ci < kChunksPerTile; ++ci) {
-                        uint32_t v[32];
-                        ptx::tc_ld_32cols(t_acc + ci * 32, v);
-                        ptx::tc_wait_ld();
-                        float s[32];
+                        for (int w = w_first + 1; w <= w_last; ++w) {   // later contributors use their "head" slot
+                            const float* src = p.scratch + static_cast<long long>(partial_slot(w, 1, CG, cta_rank)) * (kBM * BN) + row_in_tile * 4;
+                            float4 ta[8], tb[8];
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(v[i]);
-#pragma unroll 1
-                        for (int wi = 0; wi < n_others; ++wi) {
-                            const int q = ci * n_others + wi;
-                            const int b = q % kSlots;
-                            fix_ok = ptx::mbar_wait_bounded(bar_fix_full + b * 8, (fix_parity >> b) & 1u, abort_flag, timeout) && fix_ok;
-                            fix_parity ^= (1u << b);
-                            const float* src = land_gen + b * (kFixChunkBytes / 4) + row_in_tile * 4;
+                            for (int j = 0; j < 8; ++j) ta[j] = ptx::ld_cg_v4(src + (c0a / 4 + j) * (kBM * 4));
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) tb[j] = ptx::ld_cg_v4(src + (c0b / 4 + j) * (kBM * 4));
 #pragma unroll
                             for (int j = 0; j < 8; ++j) {
-                                const float4 t = *reinterpret_cast<const float4*>(src + j * (kBM * 4));
-                                s[4 * j] += t.x; s[4 * j + 1] += t.y; s[4 * j + 2] += t.z; s[4 * j + 3] += t.w;
-                            }
-                            if (q + kSlots < n_chunks) {          // the slot is needed again: refill once everyone has read it
-                                ptx::named_bar_sync(1, 128);
-                                if (epi_tid == 0) issue(q + kSlots);
+                                sa[4 * j] += ta[j].x; sa[4 * j + 1] += ta[j].y; sa[4 * j + 2] += ta[j].z; sa[4 * j + 3] += ta[j].w;
+                                sb[4 * j] += tb[j].x; sb[4 * j + 1] += tb[j].y; sb[4 * j + 2] += tb[j].z; sb[4 * j + 3] += tb[j].w;
                             }
                         }
-                        if (row < p.M && fix_ok) emit32(ci * 32, s);
+                        if (row < p.M) {
+                            emit32(c0a, sa);
+                            emit32(c0b, sb);
+                        }
+                    };
+                    if constexpr (kAccOverlap) {
+#pragma unroll
+                        for (int pos = 0; pos < kReleaseAfter; pos += 2) {
+                            float sa[32], sb[32];
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) { sa[i] = __uint_as_float(held[pos][i]); sb[i] = __uint_as_float(held[pos + 1][i]); }
+                            add_others_and_emit(chunk_at(pos) * 32, chunk_at(pos + 1) * 32, sa, sb);
+                        }
                     }
-                    release_acc();
+#pragma unroll 1
+                    for (int pos = kAccOverlap ? kReleaseAfter : 0; pos < kChunks; pos += 2) {
+                        uint32_t va[32], vb[32];
+                        ptx::tc_ld_32cols(t_acc + chunk_at(pos) * 32, va);
+                        ptx::tc_ld_32cols(t_acc + chunk_at(pos + 1) * 32, vb);
+                        ptx::tc_wait_ld();
+                        float sa[32], sb[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) { sa[i] = __uint_as_float(va[i]); sb[i] = __uint_as_float(vb[i]); }
+                        add_others_and_emit(chunk_at(pos) * 32, chunk_at(pos + 1) * 32, sa, sb);
+                    }
+                    if constexpr (!kAccOverlap) release_acc();
                     if (epi_tid == 0) *counter = 0;
                 }
             }
             ++acc_it;
-            u += k1 - k0;
         }
         if constexpr (TMA_STORE) {
             if (lane == 0) ptx::bulk_wait_group<0>();  // staging must outlive the stores that read it

@@ -944,6 +944,20 @@ int nvfp4_plan_units(int total_units, int grid, int cta, int* begin, int* end, i
     return NVFP4_OK;
 }
 
+int nvfp4_plan_segment(int total_units, int grid, int cta, int k_tiles, int index, int* begin, int* end) {
+    if (total_units < 1 || grid < 1 || cta < 0 || cta >= grid || k_tiles < 1 || index < 0 || !begin || !end)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "bad segment query");
+    Segment seg;
+    const SegmentPlan plan(unit_boundary(cta, grid, total_units), unit_boundary(cta + 1, grid, total_units), k_tiles);
+    if (!plan.at(index, &seg)) {
+        *begin = *end = -1;
+        return NVFP4_OK;
+    }
+    *begin = seg.u0;
+    *end = seg.u1;
+    return NVFP4_OK;
+}
+
 int nvfp4_plan_tile(int total_units, int workers, int k_tiles, int tiles_m, int tiles_n, int raster_rows, int tile, int* batch,
                     int* row_tile, int* col_tile) {
     if (total_units < 1 || workers < 1 || k_tiles < 1 || tiles_m < 1 || tiles_n < 1 || total_units % k_tiles || tile < 0 ||

@@ -108,6 +108,39 @@ def test_work_partition_covers_every_unit_once_and_is_balanced(lib, total, grid,
     assert lib.nvfp4_plan_units(total, grid, grid, ctypes.byref(b), ctypes.byref(e), None, kt) == _lib.NVFP4_ERR_INVALID_ARGUMENT
 
 
+@pytest.mark.parametrize("total,grid,kt", [(448 * 28, 74, 28), (3584 * 32, 74, 32), (56 * 64, 148, 64), (7, 7, 1), (100, 148, 4), (2 * 28, 148, 28), (5 * 8, 3, 8)])
+def test_segment_order_partitions_a_workers_range_and_ends_on_a_whole_tile(lib, total, grid, kt):
+    grid = min(grid, total)
+    b, e, sb, se = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    covered = [0] * total
+    for cta in range(grid):
+        assert lib.nvfp4_plan_units(total, grid, cta, ctypes.byref(b), ctypes.byref(e), None, kt) == 0
+        segs = []
+        for i in range(total // kt + 4):
+            assert lib.nvfp4_plan_segment(total, grid, cta, kt, i, ctypes.byref(sb), ctypes.byref(se)) == 0
+            if sb.value < 0:
+                break
+            segs.append((sb.value, se.value))
+        else:
+            raise AssertionError("the segment sequence does not end")
+        assert sorted(segs)[0][0] == b.value and sorted(segs)[-1][1] == e.value
+        for u0, u1 in segs:
+            assert u0 < u1 and u0 // kt == (u1 - 1) // kt                     # inside one tile
+            for u in range(u0, u1):
+                covered[u] += 1
+        whole = [sg for sg in segs if sg[1] - sg[0] == kt]
+        assert whole == sorted(whole)
+        if b.value % kt and segs:                                             # published partial: first of all
+            assert segs[0][0] == b.value
+        if e.value % kt and (e.value // kt) * kt >= b.value + ((-b.value) % kt):   # finished partial ...
+            tail = ((e.value // kt) * kt, e.value)
+            if tail[0] >= b.value:
+                pos = segs.index(tail)
+                assert pos == (len(segs) - 2 if whole else len(segs) - 1)     # ... last but one, before the last whole tile
+    assert covered == [1] * total
+    assert lib.nvfp4_plan_segment(total, grid, grid, kt, 0, ctypes.byref(sb), ctypes.byref(se)) == _lib.NVFP4_ERR_INVALID_ARGUMENT
+
+
 def test_bench_roofline_arithmetic_matches_the_stated_work():
     """Algorithmic flops / bytes per launch that bench.py divides by the measured time: the
     figures of the task's configurations (2*M*N*K*L and the packed operand, scale and output bytes)."""
