@@ -339,10 +339,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
     }
 
 
-    // Warps 0 and 1 run their loops with all 32 lanes converged and hand the single-thread
-    // instructions (TMA, tcgen05) to one lane chosen by elect.sync: the compiler then knows the
-    // issuing path is warp-uniform and feeds the descriptors straight from uniform registers.
-    // (Issuing from "if (lane == 0)" costs ~50 cycles per instruction instead.)
+    // Warps 0 and 1 each hand their whole loop to ONE lane chosen once by elect.sync (the compiler
+    // then knows the path has a single thread and feeds descriptors straight from uniform
+    // registers; a lane picked by "if (lane == 0)" costs ~50 cycles per instruction instead).
+    // Running the loop with all 32 lanes converged and electing per stage costs a vote, an
+    // election and a reconvergence per stage: 2 % of the run time of a large GEMM.
     if (warp == 0) {
         // ------------------------------------------------------------ producer
         // A is re-read by every n-tile (keep it in L2); B streams through once per m-tile.
@@ -413,6 +414,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
             uint32_t stage = 0, phase = 0, acc_it = 0, sf_it = 0;
             bool ok = true;
             Segment seg;
+            // Shared-memory descriptors of slot 0; every other one is a 32-bit add away (the address
+            // field, in 16-byte units, never carries out of its 14 bits inside 227 KB).
+            const uint64_t desc_ab0 = ptx::smem_desc_sw128(smem_base);
+            const uint64_t desc_sf0 = ptx::smem_desc_sf(smem_base + S::kABytes + S::kBBytes);
+            const uint32_t ab_lo0 = static_cast<uint32_t>(desc_ab0), ab_hi = static_cast<uint32_t>(desc_ab0 >> 32);
+            const uint32_t sf_lo0 = static_cast<uint32_t>(desc_sf0), sf_hi = static_cast<uint32_t>(desc_sf0 >> 32);
+            if (ptx::elect_one()) {
             for (int si = 0; ok && plan.at(si, &seg); ++si) {
                 const int k0 = seg.u0 - seg.tile * KT;
                 const int k1 = k0 + (seg.u1 - seg.u0);
@@ -424,80 +432,55 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                 const uint32_t empty_phase = kAccOverlap ? (acc_it & 1u) : ((acc_it / kNumAcc) & 1u);
                 {
                     ok = ptx::mbar_wait_bounded(empty_bar, empty_phase ^ 1u, abort_flag, timeout);
-                    ok = __all_sync(0xffffffffu, ok);
                 }
                 if (!ok) break;
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * S::kAccStride;
-                // When the slot after the next one to consume has landed too, both are issued as one
-                // group: one wait / vote / fence, one elected issue region and one pair of commits
-                // cover eight MMAs.  A tcgen05.commit holds up the issuing thread for about 90
-                // cycles and the wait-vote-fence sequence for as long again, which on top of the
-                // 12 + 4 instructions of a 256-wide stage exceeds the 512 cycles its MMAs run.  The
-                // second slot is only probed, never waited for: when the loads are just in time
-                // (the usual case in steady state) the stages are issued one by one.
-                for (int kt = k0; kt < k1;) {
-                    const uint32_t stage2 = (stage + 1 == STAGES) ? 0u : stage + 1;
-                    const uint32_t phase2 = (stage + 1 == STAGES) ? phase ^ 1u : phase;
+                // One stage per turn: wait, fence, 12 scale copies + 4 MMAs, commit.  The issuing thread
+                // is the critical resource of the 256-wide kernels (its turn takes about as long as the
+                // 512 cycles the MMAs of a stage run), so nothing else happens here: issuing two landed
+                // stages per turn to save a wait was tried and cost 2 % (the probe for the second
+                // stage costs what the wait saves), so did votes across a converged warp.
+                for (int kt = k0; kt < k1; ++kt) {
                     ok = ptx::mbar_wait_bounded(bar_full + stage * 8, phase, abort_flag, timeout);
-                    const bool second = (kt + 1 < k1) && ptx::mbar_test_wait(bar_full + stage2 * 8, phase2);
-                    const int group = __all_sync(0xffffffffu, second) ? 2 : 1;
-                    ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     ptx::tc_fence_after();
-                    if (ptx::elect_one()) {
+                    const uint32_t slot_off = stage * (S::kStageBytes >> 4);
+                    const uint32_t a_lo = ab_lo0 + slot_off, b_lo = a_lo + (S::kABytes >> 4);
+                    const uint32_t sfa_lo = sf_lo0 + slot_off, sfb_lo = sfa_lo + (S::kSfaBytes >> 4);
+                    const uint32_t sf_buf = sf_it & 1u;
+                    const uint32_t t_sfa = tmem_base + kSfaCol + sf_buf * 16;
+                    const uint32_t t_sfb = tmem_base + kSfbCol + sf_buf * (kMmaPerStage * kSfbColsPerMma);
+                    // With cta_group::2 each of these runs in both CTAs of the pair, every CTA reading
+                    // its own shared memory at the same offsets.
 #pragma unroll
-                        for (int g = 0; g < 2; ++g) {
-                            if (g < group) {
-                                const uint32_t slot = (g == 0) ? stage : stage2;
-                                const uint32_t sa = smem_base + slot * S::kStageBytes;
-                                const uint32_t sb = sa + S::kABytes;
-                                const uint32_t ssfa = sb + S::kBBytes;
-                                const uint32_t ssfb = ssfa + S::kSfaBytes;
-                                const uint32_t sf_buf = (sf_it + g) & 1u;
-                                const uint32_t t_sfa = tmem_base + kSfaCol + sf_buf * 16;
-                                const uint32_t t_sfb = tmem_base + kSfbCol + sf_buf * (kMmaPerStage * kSfbColsPerMma);
-                                // With cta_group::2 each of these runs in both CTAs of the pair, every CTA
-                                // reading its own shared memory at the same offsets.
+                    for (int kb = 0; kb < kMmaPerStage; ++kb) {
+                        ptx::tc_cp_sf<CG>(t_sfa + kb * 4, sfa_lo + kb * (kSfAtomBytes >> 4), sf_hi);
 #pragma unroll
-                                for (int kb = 0; kb < kMmaPerStage; ++kb) {
-                                    ptx::tc_cp_sf<CG>(t_sfa + kb * 4, ptx::smem_desc_sf(ssfa + kb * kSfAtomBytes));
-#pragma unroll
-                                    for (int h = 0; h < BN / 128; ++h)
-                                        ptx::tc_cp_sf<CG>(t_sfb + kb * kSfbColsPerMma + h * 4,
-                                                          ptx::smem_desc_sf(ssfb + h * S::kSfaBytes + kb * kSfAtomBytes));
-                                }
-                                const uint64_t a_desc = ptx::smem_desc_sw128(sa);
-                                const uint64_t b_desc = ptx::smem_desc_sw128(sb);
-#pragma unroll
-                                for (int kb = 0; kb < kMmaPerStage; ++kb) {
-                                    // K advances 64 elements = 32 bytes inside the 128-byte swizzle row: +2 in
-                                    // the (address >> 4) field of the descriptors.
-                                    ptx::tc_mma_nvf4<CG>(d_tmem, a_desc + 2 * kb, b_desc + 2 * kb, idesc, t_sfa + kb * 4,
-                                                         t_sfb + kb * kSfbColsPerMma, (kt + g > k0 || kb > 0) ? 1u : 0u);
-                                }
-                            }
-                        }
-                        // the slots are reusable (in both CTAs) once these MMAs and copies retire
-                        if constexpr (CG == 2) ptx::tc_commit_pair(bar_empty + stage * 8, 0x3);
-                        else ptx::tc_commit(bar_empty + stage * 8);
-                        if (group == 2) {
-                            if constexpr (CG == 2) ptx::tc_commit_pair(bar_empty + stage2 * 8, 0x3);
-                            else ptx::tc_commit(bar_empty + stage2 * 8);
-                        }
-                        if (kt + group == k1) {  // last k-tiles of the segment: publish the accumulator
-                            if constexpr (CG == 2) ptx::tc_commit_pair(bar_acc_full + acc * 8, 0x3);
-                            else ptx::tc_commit(bar_acc_full + acc * 8);
-                        }
+                        for (int h = 0; h < BN / 128; ++h)
+                            ptx::tc_cp_sf<CG>(t_sfb + kb * kSfbColsPerMma + h * 4, sfb_lo + h * (S::kSfaBytes >> 4) + kb * (kSfAtomBytes >> 4), sf_hi);
                     }
-                    __syncwarp();
-                    sf_it += group;
-                    for (int g = 0; g < group; ++g)
-                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-                    kt += group;
+#pragma unroll
+                    for (int kb = 0; kb < kMmaPerStage; ++kb) {
+                        // K advances 64 elements = 32 bytes inside the 128-byte swizzle row: +2 in the
+                        // (address >> 4) field of the descriptors.
+                        ptx::tc_mma_nvf4<CG>(d_tmem, a_lo + 2 * kb, b_lo + 2 * kb, ab_hi, idesc, t_sfa + kb * 4, t_sfb + kb * kSfbColsPerMma,
+                                             (kt > k0 || kb > 0) ? 1u : 0u);
+                    }
+                    // the slot is reusable (in both CTAs) once these MMAs and copies retire
+                    if constexpr (CG == 2) ptx::tc_commit_pair(bar_empty + stage * 8, 0x3);
+                    else ptx::tc_commit(bar_empty + stage * 8);
+                    if (kt + 1 == k1) {  // last k-tile of the segment: publish the accumulator
+                        if constexpr (CG == 2) ptx::tc_commit_pair(bar_acc_full + acc * 8, 0x3);
+                        else ptx::tc_commit(bar_acc_full + acc * 8);
+                    }
+                    ++sf_it;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
                 ++acc_it;
             }
+            }
+            __syncwarp();
         }
         // (the second CTA of a pair has nothing to issue: the leader's instructions drive both)
     } else {
