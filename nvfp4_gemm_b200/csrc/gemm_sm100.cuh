@@ -727,7 +727,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                     if (row < p.M) emit32(ks_rank * kMyCols + c0, s);
                 }
                 release_acc();
-            } else if (whole_tile) {
+            } else if (TMA_STORE && whole_tile) {
                 if constexpr (TMA_STORE) {
                     // 64 columns (128 bytes of fp16) at a time through a swizzled 32-row staging buffer.
                     uint8_t* staging_gen = smem_gen + S::kEpiOff + (warp - 2) * S::kStagingPerWarp;
@@ -795,45 +795,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                         }
                         store_buf = (store_buf + 1u) % S::kStagingBufs;
                     }
-                } else {
-                    // Everything the hand-back waits for goes to registers first (at most four
-                    // 32-column pieces), the accumulator is released, and only then the pieces are
-                    // converted and stored: the conversions (the re-quantising epilogue divides) must
-                    // not sit between the MMA warp and its accumulator.
-                    uint32_t held[kReleaseAfter][32];
-#pragma unroll
-                    for (int pos = 0; pos < kReleaseAfter; ++pos) ptx::tc_ld_32cols(t_acc + chunk_at(pos) * 32, held[pos]);
-                    ptx::tc_wait_ld();
-                    release_acc();
-#pragma unroll
-                    for (int pos = 0; pos < kReleaseAfter; ++pos) {
-                        if (row < p.M) {
-                            float s[32];
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(held[pos][i]);
-                            emit32(chunk_at(pos) * 32, s);
-                        }
-                    }
-#pragma unroll 1
-                    for (int pos = kReleaseAfter; pos < kChunks; ++pos) {
-                        const int c0 = chunk_at(pos) * 32;
-                        uint32_t v[32];
-                        ptx::tc_ld_32cols(t_acc + c0, v);
-                        ptx::tc_wait_ld();
-                        if (row < p.M) {
-                            float s[32];
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(v[i]);
-                            emit32(c0, s);
-                        }
-                    }
                 }
             } else {
-                // Tile shared with other workers.  Whoever holds the START of the tile's k-range
+                // A tile shared with other workers: whoever holds the START of the tile's k-range
                 // finishes the tile; everyone else publishes an fp32 partial.  The others hold the
                 // tile at the start of their ranges and contract it first of all, the finisher holds
-                // it at the end of its range and contracts it last but one.
-                const int w_first = unit_owner(tile * KT, n_workers, p.total_units);
+                // it at the end of its range and contracts it last but one.  Whole tiles of the
+                // kernels that store without TMA take the finisher's path too, with nobody else's
+                // partials to add: one copy of the (long, when it re-quantises) store code serves both,
+                // and the path that runs once per launch does not fetch 30 KB of cold instructions.
+                const int w_first = whole_tile ? worker : unit_owner(tile * KT, n_workers, p.total_units);
                 int* counter = p.counters + w_first * CG + cta_rank;
                 if (k0 > 0) {
                     // Publish.  Slot layout [BN/4][128 rows][4] keeps every warp-wide 16-byte access
@@ -874,31 +845,33 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                     // ascending worker order.  The operand ring keeps this SM's path from L2 busy,
                     // so a load issued here comes back after a microsecond or more: 64 columns of a
                     // contributor (64 registers) are requested before anything is added.
-                    const int w_last = unit_owner(tile * KT + KT - 1, n_workers, p.total_units);
+                    const int w_last = whole_tile ? w_first : unit_owner(tile * KT + KT - 1, n_workers, p.total_units);
                     const int need = KT - (k1 - k0);
-                    // The half an overlapped accumulator shares with the other one goes to registers
-                    // and is handed back before anything is waited for: the MMA warp moves on.
-                    uint32_t held[kAccOverlap ? kReleaseAfter : 1][32];
-                    if constexpr (kAccOverlap) {
+                    // Everything the hand-back waits for goes to registers first (the half an
+                    // overlapped accumulator shares with the other one, else all of it: at most four
+                    // 32-column pieces), the accumulator is released, and only then anything is
+                    // waited for, converted or stored.
+                    uint32_t held[kReleaseAfter][32];
 #pragma unroll
-                        for (int pos = 0; pos < kReleaseAfter; ++pos) ptx::tc_ld_32cols(t_acc + chunk_at(pos) * 32, held[pos]);
-                        ptx::tc_wait_ld();
-                        release_acc();
-                    }
-                    bool ready = true;
-                    if (epi_tid == 0) {
-                        const long long t_spin = clock64();
-                        while (ptx::ld_acquire_gpu(counter) < need) {
-                            if (*abort_flag || static_cast<uint64_t>(clock64() - t_spin) > timeout) {
-                                *abort_flag = 1u;
-                                ready = false;
-                                break;
+                    for (int pos = 0; pos < kReleaseAfter; ++pos) ptx::tc_ld_32cols(t_acc + chunk_at(pos) * 32, held[pos]);
+                    ptx::tc_wait_ld();
+                    release_acc();
+                    if (!whole_tile) {
+                        bool ready = true;
+                        if (epi_tid == 0) {
+                            const long long t_spin = clock64();
+                            while (ptx::ld_acquire_gpu(counter) < need) {
+                                if (*abort_flag || static_cast<uint64_t>(clock64() - t_spin) > timeout) {
+                                    *abort_flag = 1u;
+                                    ready = false;
+                                    break;
+                                }
+                                __nanosleep(64);
                             }
-                            __nanosleep(64);
                         }
+                        if (!ptx::named_bar_and(1, 128, ready)) break;
                     }
-                    if (!ptx::named_bar_and(1, 128, ready)) break;
-                    static_assert(kChunks % 2 == 0, "the partial sums are added 64 columns at a time");
+                    static_assert(kChunks % 2 == 0 && kReleaseAfter % 2 == 0, "the partial sums are added 64 columns at a time");
                     // the columns [c0a, c0a + 32) and [c0b, c0b + 32) of this thread's row: own sums in, total out
                     auto add_others_and_emit = [&](int c0a, int c0b, float (&sa)[32], float (&sb)[32]) {
 #pragma unroll 1
@@ -920,17 +893,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                             emit32(c0b, sb);
                         }
                     };
-                    if constexpr (kAccOverlap) {
 #pragma unroll
-                        for (int pos = 0; pos < kReleaseAfter; pos += 2) {
-                            float sa[32], sb[32];
+                    for (int pos = 0; pos < kReleaseAfter; pos += 2) {
+                        float sa[32], sb[32];
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) { sa[i] = __uint_as_float(held[pos][i]); sb[i] = __uint_as_float(held[pos + 1][i]); }
-                            add_others_and_emit(chunk_at(pos) * 32, chunk_at(pos + 1) * 32, sa, sb);
-                        }
+                        for (int i = 0; i < 32; ++i) { sa[i] = __uint_as_float(held[pos][i]); sb[i] = __uint_as_float(held[pos + 1][i]); }
+                        add_others_and_emit(chunk_at(pos) * 32, chunk_at(pos + 1) * 32, sa, sb);
                     }
 #pragma unroll 1
-                    for (int pos = kAccOverlap ? kReleaseAfter : 0; pos < kChunks; pos += 2) {
+                    for (int pos = kReleaseAfter; pos < kChunks; pos += 2) {
                         uint32_t va[32], vb[32];
                         ptx::tc_ld_32cols(t_acc + chunk_at(pos) * 32, va);
                         ptx::tc_ld_32cols(t_acc + chunk_at(pos + 1) * 32, vb);
@@ -940,8 +911,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                         for (int i = 0; i < 32; ++i) { sa[i] = __uint_as_float(va[i]); sb[i] = __uint_as_float(vb[i]); }
                         add_others_and_emit(chunk_at(pos) * 32, chunk_at(pos + 1) * 32, sa, sb);
                     }
-                    if constexpr (!kAccOverlap) release_acc();
-                    if (epi_tid == 0) *counter = 0;
+                    if (!whole_tile && epi_tid == 0) *counter = 0;
                 }
             }
             ++acc_it;
