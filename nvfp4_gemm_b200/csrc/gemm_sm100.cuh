@@ -91,6 +91,7 @@ struct GemmParams {
     int total_units;                // tiles_m * tiles_n * L * k_tiles
 };
 
+constexpr int kPrefetchStages = 2;                  // stages of a CTA's first segment prefetched into L2 ahead of the dependency wait
 constexpr int kGlobalExchangeMinSplit = 4;         // cluster split-K: from this split on the partial sums travel through L2
 constexpr int kScratchSlotFloats = kBM * 256;      // one partial-tile slot of the library's scratch (128 x 256 fp32)
 
@@ -326,6 +327,27 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
     Segment first_seg{0, 0, 0};
     plan.at(0, &first_seg);
     const TileCoord first_tc = tile_coords(first_seg.tile, n_workers, KT, p.total_units, p.tiles_m, p.tiles_n, (KS > 1) ? 0 : p.raster_rows);
+    // The operands of this CTA's first two stages are asked into L2 now, ahead of the dependency wait:
+    // a CTA of a back-to-back launch reaches this point while slower CTAs of the previous launch
+    // are still running, and its first loads then find their lines in L2 instead of paying the
+    // DRAM latency after the wait.  A prefetch consumes nothing: lines the previous launch still
+    // writes are updated in L2, where the loads read them.  (Two stages: asking for the whole ring
+    // takes HBM bandwidth from the tail of the previous launch and made the decode shape slower.)
+    if (warp == 0 && first_seg.u1 > first_seg.u0) {
+        if (ptx::elect_one()) {
+            const int k0 = first_seg.u0 - first_seg.tile * KT;
+            const int n_pre = min(kPrefetchStages, first_seg.u1 - first_seg.u0);
+            const int mb = first_tc.mt * CG + cta_rank;
+            for (int i = 0; i < n_pre; ++i) {
+                const int kt = k0 + i;
+                ptx::tma_prefetch_3d(&p.tma_a, kt * kBKBytes, mb * kBM, first_tc.l);
+                ptx::tma_prefetch_3d(&p.tma_b, kt * kBKBytes, first_tc.nt * BN + cta_rank * kBRows, first_tc.l);
+                ptx::tma_prefetch_4d(&p.tma_sfa, 0, kt * kMmaPerStage, mb, first_tc.l);
+                ptx::tma_prefetch_4d(&p.tma_sfb, 0, kt * kMmaPerStage, first_tc.nt * (BN / 128), first_tc.l);
+            }
+        }
+        __syncwarp();
+    }
     // Kernels of this library are often launched back to back (a decode step is a chain of short
     // GEMMs): let the next launch's CTAs set up (barriers, TMEM, descriptor prefetch) on SMs this
     // grid leaves idle or frees, and touch global memory only after everything the stream ordered
@@ -430,9 +452,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                 // earlier by the same threads).  Plain: one barrier per accumulator.
                 const uint32_t empty_bar = bar_acc_empty + (kAccOverlap ? 0u : acc * 8);
                 const uint32_t empty_phase = kAccOverlap ? (acc_it & 1u) : ((acc_it / kNumAcc) & 1u);
-                {
-                    ok = ptx::mbar_wait_bounded(empty_bar, empty_phase ^ 1u, abort_flag, timeout);
-                }
+                ok = ptx::mbar_wait_bounded(empty_bar, empty_phase ^ 1u, abort_flag, timeout);
                 if (!ok) break;
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * S::kAccStride;
