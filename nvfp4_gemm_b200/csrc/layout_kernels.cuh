@@ -156,42 +156,95 @@ __global__ void __launch_bounds__(256) scales_from_permuted_kernel(const uint8_t
 }
 
 // NVFP4 quantiser (the step before the matmul): fp16 / bf16 [rows][K] -> packed e2m1 + one e4m3
-// scale per 16 elements, scale = RN(max|x| / 6), element = RN(x / scale) saturated to +-6.  One
-// thread owns one 16-element block: 32 bytes in, 8 bytes + one scale byte out (plain layout and /
-// or the permuted 128 x 4 atom layout).
-template <bool BF16>
+// scale per 16 elements, scale = RN(max|x| / 6), element = RN(x / scale) saturated to +-6.
+// Work unit: 128 rows x 256 columns (one row block of the permuted scale layout x 4 of its atoms),
+// taken in turn by a grid of resident CTAs of 256 threads.  A thread owns 64 consecutive elements of
+// a row = four scale blocks = one 4-byte unit of both scale layouts: 128 bytes in (eight 16-byte
+// loads, all in flight before the first block is worked on; four neighbouring threads cover 512
+// bytes of a row), 32 bytes of codes and the 4-byte word of plain scales out.  The permuted scales
+// of the unit -- 4 atoms of 512 bytes, contiguous in memory -- are collected in shared memory and
+// written as whole 16-byte pieces (written from the threads' rows they would be 4-byte pieces
+// scattered over the atoms: 10 % of the run time); rows of the block that do not exist are written
+// as zero scales.
+// kWide: every output address is aligned for the wide stores (16 bytes for the codes and the
+// permuted scales, 4 bytes for the plain scale words); otherwise 8-byte and single-byte stores.
+constexpr int kQuantGroups = 4;   // 64-element groups (= scale atoms) along K per work unit
+template <bool BF16, bool kWide>
 __global__ void __launch_bounds__(256) quantize_nvfp4_kernel(const void* __restrict__ x, uint8_t* __restrict__ packed,
                                                              uint8_t* __restrict__ sf_plain, uint8_t* __restrict__ sf_perm, int rows,
                                                              int k, long long x_row_stride, long long packed_row_stride,
                                                              long long sf_plain_row_stride) {
-    const int blocks_per_row = k / 16;
-    const long long total = static_cast<long long>(rows) * blocks_per_row;
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const int row = static_cast<int>(i / blocks_per_row);
-        const int blk = static_cast<int>(i - static_cast<long long>(row) * blocks_per_row);
-        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + row * x_row_stride + blk * 16);
-        const uint4 lo = __ldcs(src), hi = __ldcs(src + 1);
-        const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-        float v[16];
+    __shared__ uint32_t staged[2][kQuantGroups][129];   // [unit parity][atom][word of the atom = (row % 32) * 4 + row / 32], padded
+    const int groups_per_row = k / 64;
+    const int units_k = (groups_per_row + kQuantGroups - 1) / kQuantGroups;
+    const long long units = static_cast<long long>((rows + 127) / 128) * units_k;
+    const int g = threadIdx.x & (kQuantGroups - 1);
+    int parity = 0;
+    for (long long unit = blockIdx.x; unit < units; unit += gridDim.x, parity ^= 1) {
+        const int row_block = static_cast<int>(unit / units_k);
+        const int unit_k = static_cast<int>(unit - static_cast<long long>(row_block) * units_k);
+        const int grp = unit_k * kQuantGroups + g;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            if (BF16) {
-                v[2 * j] = __uint_as_float(w[j] << 16);
-                v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
-            } else {
-                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
-                v[2 * j] = f.x;
-                v[2 * j + 1] = f.y;
+        for (int it = 0; it < 128 * kQuantGroups / 256; ++it) {
+            const int r = it * (256 / kQuantGroups) + threadIdx.x / kQuantGroups;   // row inside the block
+            const long long row = static_cast<long long>(row_block) * 128 + r;
+            uint32_t scales = 0u;
+            if (row < rows && grp < groups_per_row) {
+                const uint8_t* src = reinterpret_cast<const uint8_t*>(static_cast<const uint16_t*>(x) + row * x_row_stride + grp * 64);
+                uint4 in[8];
+#pragma unroll
+                for (int b = 0; b < 8; ++b) in[b] = __ldcs(reinterpret_cast<const uint4*>(src) + b);
+                uint32_t codes[8];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    const uint32_t w[8] = {in[2 * b].x, in[2 * b].y, in[2 * b].z, in[2 * b].w, in[2 * b + 1].x, in[2 * b + 1].y, in[2 * b + 1].z, in[2 * b + 1].w};
+                    float v[16];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        if (BF16) {
+                            v[2 * j] = __uint_as_float(w[j] << 16);
+                            v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+                        } else {
+                            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+                            v[2 * j] = f.x;
+                            v[2 * j + 1] = f.y;
+                        }
+                    }
+                    uint32_t out[2];
+                    const uint32_t sf_byte = quantize_block16(v, out);
+                    codes[2 * b] = out[0];
+                    codes[2 * b + 1] = out[1];
+                    scales |= sf_byte << (8 * b);
+                }
+                uint8_t* dst = packed + row * packed_row_stride + grp * 32;
+                if (kWide) {
+                    *reinterpret_cast<uint4*>(dst) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+                    *reinterpret_cast<uint4*>(dst + 16) = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+                    if (sf_plain) *reinterpret_cast<uint32_t*>(sf_plain + row * sf_plain_row_stride + grp * 4) = scales;
+                } else {
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) {
+                        *reinterpret_cast<uint2*>(dst + 8 * b) = make_uint2(codes[2 * b], codes[2 * b + 1]);
+                        if (sf_plain) sf_plain[row * sf_plain_row_stride + grp * 4 + b] = static_cast<uint8_t>(scales >> (8 * b));
+                    }
+                }
             }
+            staged[parity][g][(r & 31) * 4 + (r >> 5)] = scales;
         }
-        uint32_t out[2];
-        const uint8_t sf_byte = quantize_block16(v, out);
-        *reinterpret_cast<uint2*>(packed + row * packed_row_stride + blk * 8) = make_uint2(out[0], out[1]);
-        if (sf_plain) sf_plain[row * sf_plain_row_stride + blk] = sf_byte;
-        if (sf_perm) {
-            const long long off = (static_cast<long long>(row / 128) * (k / 64) + blk / 4) * 512 + (row % 32) * 16 + ((row / 32) % 4) * 4 + (blk % 4);
-            sf_perm[off] = sf_byte;
+        if (sf_perm == nullptr) continue;
+        __syncthreads();   // (the other parity's buffer is written next: one barrier per unit is enough)
+        // the unit's atoms are contiguous: [row block][atom along K][512 bytes]
+        const int atoms_here = min(kQuantGroups, groups_per_row - unit_k * kQuantGroups);
+        const int atom = threadIdx.x >> 5, piece = threadIdx.x & 31;   // 16-byte piece of an atom
+        if (atom < atoms_here) {
+            uint8_t* dst = sf_perm + (static_cast<long long>(row_block) * groups_per_row + unit_k * kQuantGroups + atom) * 512 + piece * 16;
+            const uint32_t* st = &staged[parity][atom][piece * 4];
+            if (kWide) {
+                *reinterpret_cast<uint4*>(dst) = make_uint4(st[0], st[1], st[2], st[3]);
+            } else {
+#pragma unroll
+                for (int b = 0; b < 16; ++b) dst[b] = static_cast<uint8_t>(st[b >> 2] >> (8 * (b & 3)));
+            }
         }
     }
 }

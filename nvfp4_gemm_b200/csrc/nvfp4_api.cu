@@ -853,27 +853,27 @@ int nvfp4_quantize(const void* x, int32_t x_is_bf16, void* packed, void* sf_plai
     if (!aligned(packed, 8) || packed_row_stride % 8 || packed_row_stride < k / 2)
         return fail(NVFP4_ERR_INVALID_ARGUMENT, "packed must be 8-byte aligned with a row stride that is a multiple of 8 and >= k/2");
     if (sf_plain && sf_plain_row_stride < k / 16) return fail(NVFP4_ERR_INVALID_ARGUMENT, "sf_plain_row_stride must be >= k/16");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     int dev = 0, sms = 0;
     CUDA_TRY(cudaGetDevice(&dev));
     CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    const long long total = static_cast<long long>(rows) * (k / 16);
-    long long grid = (total + 255) / 256;
-    if (grid > static_cast<long long>(sms) * 16) grid = static_cast<long long>(sms) * 16;
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    if (sf_permuted && rows % 128) {
-        // rows of the last 128-row block that do not exist must read as zero scales
-        const long long bytes = static_cast<long long>((rows + 127) / 128) * (k / 64) * 512;
-        const long long tail = static_cast<long long>(k / 64) * 512;
-        CUDA_TRY(cudaMemsetAsync(static_cast<uint8_t*>(sf_permuted) + bytes - tail, 0, tail, stream));
+    // resident CTAs take 128-row x 256-column units in turn
+    const long long units = static_cast<long long>((rows + 127) / 128) * ((k / 64 + kQuantGroups - 1) / kQuantGroups);
+    const int grid = static_cast<int>(units < static_cast<long long>(sms) * 4 ? units : static_cast<long long>(sms) * 4);
+    // wide stores when every output address is aligned for them
+    const bool wide = aligned(packed, 16) && packed_row_stride % 16 == 0 && (!sf_plain || (aligned(sf_plain, 4) && sf_plain_row_stride % 4 == 0)) &&
+                      (!sf_permuted || aligned(sf_permuted, 16));
+    auto launch = [&](auto kernel) {
+        kernel<<<grid, 256, 0, stream>>>(x, static_cast<uint8_t*>(packed), static_cast<uint8_t*>(sf_plain), static_cast<uint8_t*>(sf_permuted), rows, k,
+                                         x_row_stride, packed_row_stride, sf_plain_row_stride);
+    };
+    if (x_is_bf16) {
+        if (wide) launch(quantize_nvfp4_kernel<true, true>);
+        else launch(quantize_nvfp4_kernel<true, false>);
+    } else {
+        if (wide) launch(quantize_nvfp4_kernel<false, true>);
+        else launch(quantize_nvfp4_kernel<false, false>);
     }
-    if (x_is_bf16)
-        quantize_nvfp4_kernel<true><<<static_cast<int>(grid), 256, 0, stream>>>(x, static_cast<uint8_t*>(packed), static_cast<uint8_t*>(sf_plain),
-                                                                               static_cast<uint8_t*>(sf_permuted), rows, k, x_row_stride,
-                                                                               packed_row_stride, sf_plain_row_stride);
-    else
-        quantize_nvfp4_kernel<false><<<static_cast<int>(grid), 256, 0, stream>>>(x, static_cast<uint8_t*>(packed), static_cast<uint8_t*>(sf_plain),
-                                                                                static_cast<uint8_t*>(sf_permuted), rows, k, x_row_stride,
-                                                                                packed_row_stride, sf_plain_row_stride);
     CUDA_TRY(cudaGetLastError());
     g_launches.fetch_add(1);
     return NVFP4_OK;

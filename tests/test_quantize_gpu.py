@@ -41,6 +41,31 @@ def test_quantizer_matches_oracle_bit_for_bit(cuda_lib, oracle, dtype, rows, k):
     assert np.array_equal(perm.cpu().numpy(), oracle.permute_sf(exp_sf[:, :, None]))
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_quantizer_with_outputs_that_only_allow_narrow_stores(cuda_lib, oracle, dtype):
+    """Codes 8 bytes off a 16-byte boundary and scale rows with an odd stride: the kernel falls back
+    from its 16-byte / 4-byte stores to 8-byte / single-byte ones."""
+    from nvfp4_gemm_b200 import _lib
+    rows, k = 200, 512
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn((rows, k), generator=g) * 3).to(dtype).cuda()
+    packed_buf = torch.zeros((rows * (k // 2 + 8) + 8,), dtype=torch.uint8, device="cuda")
+    packed = packed_buf[8:]                                   # 8-byte aligned only, row stride k/2 + 8
+    sf_buf = torch.zeros((rows * (k // 16 + 1) + 1,), dtype=torch.uint8, device="cuda")
+    sf = sf_buf[1:]                                           # odd base address, odd row stride
+    perm = torch.full((((rows + 127) // 128) * (k // 64) * 512,), 0xEE, dtype=torch.uint8, device="cuda")
+    _lib.check(cuda_lib.nvfp4_quantize(x.data_ptr(), int(dtype == torch.bfloat16), packed.data_ptr(), sf.data_ptr(), perm.data_ptr(),
+                                       rows, k, x.stride(0), k // 2 + 8, k // 16 + 1, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    exp_packed, exp_sf = oracle.quantize_rows(x.float().cpu().numpy())
+    got_packed = packed[: rows * (k // 2 + 8)].view(rows, k // 2 + 8)[:, : k // 2].cpu().numpy()
+    got_sf = sf[: rows * (k // 16 + 1)].view(rows, k // 16 + 1)[:, : k // 16].cpu().numpy()
+    assert np.array_equal(got_packed, exp_packed)
+    assert np.array_equal(got_sf, exp_sf)
+    assert np.array_equal(perm.cpu().numpy(), oracle.permute_sf(exp_sf[:, :, None]))
+    assert int(packed_buf[:8].sum()) == 0 and int(sf_buf[0]) == 0          # nothing written in front of the buffers
+
+
 def _e4m3_positive():
     vals = []
     for byte in range(1, 127):
