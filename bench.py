@@ -35,7 +35,7 @@ WORKLOADS = {
 }
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
 # captures summarised under profiles/ (one capture per kernel and workload).
-NCU_DRAM_BYTES_PER_LAUNCH = {"c1": 68.6e6, "c2": 268.0e6, "c3": 130.3e6, "c4": 802.2e6}
+NCU_DRAM_BYTES_PER_LAUNCH = {"c1": 68.3e6, "c2": 268.0e6, "c3": 132.3e6, "c4": 804.6e6}
 # The reference task's other timed shapes with the speed-of-light figures its statement gives for
 # them (task.yml:29-33, task_gemv.yml:29-33: max(math, DRAM) of a B200 at 1.5 GHz), reported as
 # extra rows beside the headline.

@@ -510,6 +510,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
         const int epi_tid = threadIdx.x - 64;  // 0..127
         uint32_t acc_it = 0;
         uint32_t store_buf = 0;
+        // NVFP4 output: whether 32-byte code stores and 4-byte scale stores are aligned
+        const bool wide_packed = EPI_EX && ((reinterpret_cast<uintptr_t>(p.out_packed) | static_cast<uintptr_t>(p.out_packed_row_stride) |
+                                              static_cast<uintptr_t>(p.out_packed_batch_stride)) & 31u) == 0;
+        const bool wide_sf = EPI_EX && ((reinterpret_cast<uintptr_t>(p.out_sf) | static_cast<uintptr_t>(p.out_sf_row_stride) |
+                                          static_cast<uintptr_t>(p.out_sf_batch_stride)) & 3u) == 0;
         Segment seg;
         for (int si = 0; plan.at(si, &seg); ++si) {
             const int tile = seg.tile;
@@ -545,63 +550,110 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
             // fp16 and store; the extended epilogue adds the bias, applies the activation and writes
             // fp16 or NVFP4.  The NVFP4 form quantises the fp16-ROUNDED values, so the result equals
             // the stand-alone quantiser run on the fp16 output.
+            // (extended epilogue) bias and activation on 32 columns starting at global column gcol
+            auto bias_act32 = [&](int gcol, float (&s)[32]) {
+                if (p.bias != nullptr) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint4 b8 = *reinterpret_cast<const uint4*>(p.bias + gcol + 8 * j);
+                        const uint32_t w[4] = {b8.x, b8.y, b8.z, b8.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+                            s[8 * j + 2 * e] = __fadd_rn(s[8 * j + 2 * e], f.x);
+                            s[8 * j + 2 * e + 1] = __fadd_rn(s[8 * j + 2 * e + 1], f.y);
+                        }
+                    }
+                }
+                if (p.activation == kActRelu) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) s[i] = fmaxf(s[i], 0.f);
+                } else if (p.activation == kActSilu) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) s[i] = __fdividef(s[i], 1.f + __expf(-s[i]));
+                }
+            };
+            // 32 values -> 16 bytes of e2m1 codes and the two e4m3 scale bytes (low byte = lower columns)
+            auto quantize32 = [&](const float (&s)[32], uint32_t (&q)[4]) {
+                uint32_t sf2 = 0u;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    float v[16];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {   // round to fp16 and back, two at a time
+                        const float2 f = __half22float2(__floats2half2_rn(s[16 * h + 2 * i], s[16 * h + 2 * i + 1]));
+                        v[2 * i] = f.x;
+                        v[2 * i + 1] = f.y;
+                    }
+                    uint32_t o[2];
+                    sf2 |= static_cast<uint32_t>(quantize_block16(v, o)) << (8 * h);
+                    q[2 * h] = o[0];
+                    q[2 * h + 1] = o[1];
+                }
+                return sf2;
+            };
+            auto packed_at = [&](int gcol) {
+                return p.out_packed + l * p.out_packed_batch_stride + static_cast<long long>(row) * p.out_packed_row_stride + gcol / 2;
+            };
+            auto sf_plain_at = [&](int gcol) { return p.out_sf + l * p.out_sf_batch_stride + static_cast<long long>(row) * p.out_sf_row_stride + gcol / 16; };
+            auto sf_perm_at = [&](int gcol) {   // scale of (row, 16-column block gcol / 16) in the 128 x 4 atom layout
+                const int blk = gcol / 16;
+                return p.out_sf_perm + l * p.out_sf_perm_batch_stride + (row / 128) * p.out_sf_perm_block_stride + (blk / 4) * 512 + (row % 32) * 16 +
+                       ((row / 32) % 4) * 4 + (blk % 4);
+            };
             auto emit32 = [&](int c0, float (&s)[32]) {
                 if constexpr (!EPI_EX) {
 #pragma unroll
                     for (int j = 0; j < 4; ++j) store8(c0 + 8 * j, pack8_fp16(&s[8 * j]));
                 } else {
                     const int gcol = nb * BN + c0;
-                    if (p.bias != nullptr) {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const uint4 b8 = *reinterpret_cast<const uint4*>(p.bias + gcol + 8 * j);
-                            const uint32_t w[4] = {b8.x, b8.y, b8.z, b8.w};
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
-                                s[8 * j + 2 * e] = __fadd_rn(s[8 * j + 2 * e], f.x);
-                                s[8 * j + 2 * e + 1] = __fadd_rn(s[8 * j + 2 * e + 1], f.y);
-                            }
-                        }
-                    }
-                    if (p.activation == kActRelu) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) s[i] = fmaxf(s[i], 0.f);
-                    } else if (p.activation == kActSilu) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) s[i] = __fdividef(s[i], 1.f + __expf(-s[i]));
-                    }
+                    bias_act32(gcol, s);
                     if (!p.out_nvfp4) {
 #pragma unroll
                         for (int j = 0; j < 4; ++j) store8(c0 + 8 * j, pack8_fp16(&s[8 * j]));
                     } else {
                         uint32_t q[4];
-                        uint8_t sf[2];
-#pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            float v[16];
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {   // round to fp16 and back, two at a time
-                                const float2 f = __half22float2(__floats2half2_rn(s[16 * h + 2 * i], s[16 * h + 2 * i + 1]));
-                                v[2 * i] = f.x;
-                                v[2 * i + 1] = f.y;
-                            }
-                            uint32_t o[2];
-                            sf[h] = quantize_block16(v, o);
-                            q[2 * h] = o[0];
-                            q[2 * h + 1] = o[1];
-                        }
-                        *reinterpret_cast<uint4*>(p.out_packed + l * p.out_packed_batch_stride + static_cast<long long>(row) * p.out_packed_row_stride +
-                                                  gcol / 2) = make_uint4(q[0], q[1], q[2], q[3]);
-                        const uint16_t sf2 = static_cast<uint16_t>(sf[0] | (sf[1] << 8));
-                        const int blk = gcol / 16;      // even: the two scales are neighbours in both layouts
-                        if (p.out_sf != nullptr)
-                            *reinterpret_cast<uint16_t*>(p.out_sf + l * p.out_sf_batch_stride + static_cast<long long>(row) * p.out_sf_row_stride + blk) = sf2;
-                        if (p.out_sf_perm != nullptr)
-                            *reinterpret_cast<uint16_t*>(p.out_sf_perm + l * p.out_sf_perm_batch_stride +
-                                                         (row / 128) * p.out_sf_perm_block_stride + (blk / 4) * 512 + (row % 32) * 16 +
-                                                         ((row / 32) % 4) * 4 + (blk % 4)) = sf2;
+                        const uint16_t sf2 = static_cast<uint16_t>(quantize32(s, q));   // two scales: neighbours in both layouts
+                        *reinterpret_cast<uint4*>(packed_at(gcol)) = make_uint4(q[0], q[1], q[2], q[3]);
+                        if (p.out_sf != nullptr) *reinterpret_cast<uint16_t*>(sf_plain_at(gcol)) = sf2;
+                        if (p.out_sf_perm != nullptr) *reinterpret_cast<uint16_t*>(sf_perm_at(gcol)) = sf2;
                     }
+                }
+            };
+            // 64 columns [c0, c0 + 64), c0 a multiple of 64.  The NVFP4 form then has 32 bytes of codes
+            // (one full sector) and the four scales of one unit of either scale layout: one store
+            // each where the addresses allow it, instead of twice two partial ones.
+            auto emit64 = [&](int c0, float (&sa)[32], float (&sb)[32]) {
+                if constexpr (!EPI_EX) {
+                    emit32(c0, sa);
+                    emit32(c0 + 32, sb);
+                } else {
+                    if (!p.out_nvfp4) {
+                        emit32(c0, sa);
+                        emit32(c0 + 32, sb);
+                        return;
+                    }
+                    const int gcol = nb * BN + c0;
+                    bias_act32(gcol, sa);
+                    bias_act32(gcol + 32, sb);
+                    uint32_t qa[4], qb[4];
+                    const uint32_t sf4 = quantize32(sa, qa) | (quantize32(sb, qb) << 16);
+                    uint8_t* dst = packed_at(gcol);
+                    if (wide_packed) {
+                        ptx::st_global_32B(dst, qa[0], qa[1], qa[2], qa[3], qb[0], qb[1], qb[2], qb[3]);
+                    } else {
+                        *reinterpret_cast<uint4*>(dst) = make_uint4(qa[0], qa[1], qa[2], qa[3]);
+                        *reinterpret_cast<uint4*>(dst + 16) = make_uint4(qb[0], qb[1], qb[2], qb[3]);
+                    }
+                    if (p.out_sf != nullptr) {
+                        if (wide_sf) {
+                            *reinterpret_cast<uint32_t*>(sf_plain_at(gcol)) = sf4;
+                        } else {
+                            *reinterpret_cast<uint16_t*>(sf_plain_at(gcol)) = static_cast<uint16_t>(sf4);
+                            *reinterpret_cast<uint16_t*>(sf_plain_at(gcol + 32)) = static_cast<uint16_t>(sf4 >> 16);
+                        }
+                    }
+                    if (p.out_sf_perm != nullptr) *reinterpret_cast<uint32_t*>(sf_perm_at(gcol)) = sf4;   // (16-byte aligned atoms: always aligned)
                 }
             };
             auto release_acc = [&]() {
@@ -908,10 +960,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                                 sb[4 * j] += tb[j].x; sb[4 * j + 1] += tb[j].y; sb[4 * j + 2] += tb[j].z; sb[4 * j + 3] += tb[j].w;
                             }
                         }
-                        if (row < p.M) {
-                            emit32(c0a, sa);
-                            emit32(c0b, sb);
-                        }
+                        if (row < p.M) emit64(c0a, sa, sb);   // (c0b == c0a + 32: drain positions pair up neighbouring chunks)
                     };
 #pragma unroll
                     for (int pos = 0; pos < kReleaseAfter; pos += 2) {

@@ -365,6 +365,15 @@ __device__ __forceinline__ float4 ld_cg_v4(const float* addr) {
 __device__ __forceinline__ void st_cg_v4(float* addr, float4 v) {
     asm volatile("st.global.cg.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
+// One 32-byte store (a full sector); addr 32-byte aligned.
+__device__ __forceinline__ void st_global_32B(void* addr, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, uint32_t w4, uint32_t w5, uint32_t w6,
+                                              uint32_t w7) {
+    asm volatile(
+        "{\n\t.reg .b64 d0, d1, d2, d3;\n\t"
+        "mov.b64 d0, {%1, %2};\n\tmov.b64 d1, {%3, %4};\n\tmov.b64 d2, {%5, %6};\n\tmov.b64 d3, {%7, %8};\n\t"
+        "st.global.v4.b64 [%0], {d0, d1, d2, d3};\n\t}"
+        ::"l"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3), "r"(w4), "r"(w5), "r"(w6), "r"(w7) : "memory");
+}
 __device__ __forceinline__ int ld_acquire_gpu(const int* addr) {
     int v;
     asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
