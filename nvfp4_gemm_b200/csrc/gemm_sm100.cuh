@@ -442,7 +442,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
             const uint64_t desc_sf0 = ptx::smem_desc_sf(smem_base + S::kABytes + S::kBBytes);
             const uint32_t ab_lo0 = static_cast<uint32_t>(desc_ab0), ab_hi = static_cast<uint32_t>(desc_ab0 >> 32);
             const uint32_t sf_lo0 = static_cast<uint32_t>(desc_sf0), sf_hi = static_cast<uint32_t>(desc_sf0 >> 32);
-            if (ptx::elect_one()) {
+            if (ptx::elect_one()) {   // (the loop below is this one thread's; indentation kept flat)
             for (int si = 0; ok && plan.at(si, &seg); ++si) {
                 const int k0 = seg.u0 - seg.tile * KT;
                 const int k1 = k0 + (seg.u1 - seg.u0);
@@ -456,11 +456,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                 if (!ok) break;
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * S::kAccStride;
-                // One stage per turn: wait, fence, 12 scale copies + 4 MMAs, commit.  The issuing thread
-                // is the critical resource of the 256-wide kernels (its turn takes about as long as the
-                // 512 cycles the MMAs of a stage run), so nothing else happens here: issuing two landed
-                // stages per turn to save a wait was tried and cost 2 % (the probe for the second
-                // stage costs what the wait saves), so did votes across a converged warp.
+                // One stage per turn: wait, fence, 12 scale copies + 4 MMAs, commit: about 200 cycles of
+                // this thread for the 512 cycles the MMAs of a 256-wide stage run, so the pipe always
+                // has a stage or two queued.  Anything more in this loop showed up in the run time:
+                // as a converged warp that polls, votes and elects per stage a turn took 650 cycles
+                // and the pipe starved; issuing two landed stages per turn to save a wait cost 2 %
+                // (the probe for the second stage costs what the wait saves).
                 for (int kt = k0; kt < k1; ++kt) {
                     ok = ptx::mbar_wait_bounded(bar_full + stage * 8, phase, abort_flag, timeout);
                     if (!ok) break;
