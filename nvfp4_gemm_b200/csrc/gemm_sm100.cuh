@@ -89,6 +89,7 @@ struct GemmParams {
     int tiles_m, tiles_n, k_tiles;  // tiles of (128*CG) x BN; k_tiles = K / 256
     int raster_rows;                // row tiles per group of the persistent kernels' tile order; 0 = row-major
     int total_units;                // tiles_m * tiles_n * L * k_tiles
+    int whole_tiles;                // 1: workers split the work at tile boundaries only (no tile is shared); raster_rows must be 0
 };
 
 constexpr int kPrefetchStages = 2;                  // stages of a CTA's first segment prefetched into L2 ahead of the dependency wait
@@ -320,8 +321,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
     const int n_workers = (KS > 1) ? static_cast<int>(gridDim.x) : static_cast<int>(gridDim.x) / CG;
     const int worker = (KS > 1) ? static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x) / CG;
     // stream-K: equal share of all units.  Cluster split-K: tile = cluster index, k-range by rank.
-    const int u_begin = (KS > 1) ? (worker / KS) * KT + (ks_rank * KT) / KS : unit_boundary(worker, n_workers, p.total_units);
-    const int u_end = (KS > 1) ? (worker / KS) * KT + ((ks_rank + 1) * KT) / KS : unit_boundary(worker + 1, n_workers, p.total_units);
+    // Whole tiles: the same even split counted in tiles (p.total_units / KT of them) instead of units.
+    const int split_total = p.whole_tiles ? p.tiles_m * p.tiles_n * p.L : p.total_units;
+    const int split_scale = p.whole_tiles ? KT : 1;
+    const int u_begin = (KS > 1) ? (worker / KS) * KT + (ks_rank * KT) / KS : unit_boundary(worker, n_workers, split_total) * split_scale;
+    const int u_end = (KS > 1) ? (worker / KS) * KT + ((ks_rank + 1) * KT) / KS : unit_boundary(worker + 1, n_workers, split_total) * split_scale;
     const uint64_t timeout = p.timeout_cycles;
     const SegmentPlan plan(u_begin, u_end, KT);   // (a cluster split-K CTA has one segment: its share of the tile's k-range)
     Segment first_seg{0, 0, 0};

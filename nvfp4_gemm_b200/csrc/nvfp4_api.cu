@@ -237,6 +237,27 @@ MapKey make_sf_key(const void* ptr, int rows, int k, int l, uint64_t batch_strid
 
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
+// Whole tiles per worker, or an even split of all (tile, k-tile) units with shared tiles summed
+// through scratch?  In k-tiles of run time: whole tiles cost waves x k_tiles; the even split costs
+// units / workers plus the summing, which hides behind later whole tiles when a worker has at
+// least two tiles' worth of units and otherwise ends the launch (publish, wait, read back:
+// measured about as long as 24 k-tiles of the 256-wide pair kernel -- 768 x 4096 x 4096 took
+// 19.5 us split 74 ways and 10.6 us as 48 whole tiles).
+struct WorkSplit {
+    double cost;        // k-tiles of run time
+    int workers;
+    bool whole_tiles;
+};
+WorkSplit plan_work_split(long long tiles, int k_tiles, int max_workers) {
+    const long long whole_workers_max = tiles < max_workers ? tiles : max_workers;
+    const long long waves = (tiles + whole_workers_max - 1) / whole_workers_max;
+    const double cost_whole = static_cast<double>(waves) * k_tiles;
+    const double share = static_cast<double>(tiles) * k_tiles / max_workers;
+    const double cost_split = share + (share >= 2.0 * k_tiles ? 3.0 : 24.0);
+    if (cost_whole <= cost_split) return WorkSplit{cost_whole, static_cast<int>((tiles + waves - 1) / waves), true};   // the fewest workers that need no more waves
+    return WorkSplit{cost_split, max_workers, false};
+}
+
 template <int CG, int BN, int STAGES, bool TMA_STORE, int EPI_KB, bool EPI_EX = false>
 int launch_gemm(DeviceCtx* c, int variant, GemmParams& params, int grid_request, cudaStream_t stream, const char* name) {
     using S = GemmSmem<CG, BN, STAGES, TMA_STORE, EPI_KB>;
@@ -279,14 +300,11 @@ int launch_gemm(DeviceCtx* c, int variant, GemmParams& params, int grid_request,
     if (grid > kMaxCtas) grid = kMaxCtas;
     int workers = grid / CG;
     if (grid_request <= 0) {
-        // Splitting a tile's K range between workers costs a round trip through global scratch,
-        // which only pays when every share keeps at least ~8 k-tiles; with fewer tiles than
-        // workers and a short K, run one whole tile per worker instead.
-        const int tiles = params.total_units / params.k_tiles;
-        if (tiles < workers) {
-            int w = params.total_units / 8;
-            if (w < tiles) w = tiles;
-            if (w < workers) workers = w;
+        const WorkSplit split = plan_work_split(params.total_units / params.k_tiles, params.k_tiles, workers);
+        workers = split.workers;
+        if (split.whole_tiles) {
+            params.whole_tiles = 1;
+            params.raster_rows = 0;
         }
     }
     if (workers > params.total_units) workers = params.total_units;
@@ -434,12 +452,25 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, const nvfp4_
     // one 128-row block; decode shapes (m <= 128) stay on single CTAs.
     int cg = cf.cta_group;
     if (cg == 0) cg = (p->m > kBM && p->n % 256 == 0) ? 2 : 1;
+    if (cf.cta_group == 0 && cf.tile_n == 0 && cg == 2 && cf.grid == 0 && cf.split_k <= 1) {
+        // 256 x 256 tiles on CTA pairs do twice the work per SM and stage of 128 x 128 tiles on
+        // single CTAs, but small problems fill more SMs with the small tiles and their epilogue is
+        // shorter.  Estimated run time in k-tiles of the pair kernel (one of its stages ~ 0.35 us;
+        // a 128-wide stage 0.9 of that, the epilogues of the last tile 9 and 4.5), constants fitted
+        // to thirteen measured shapes from 256 x 7168 x 256 to 4096 x 7168 x 7168.
+        const int k_tiles = p->k / kKPerStage;
+        const long long tiles256 = static_cast<long long>((p->m + 2 * kBM - 1) / (2 * kBM)) * (p->n / 256) * p->l;
+        const long long tiles128 = static_cast<long long>((p->m + kBM - 1) / kBM) * (p->n / 128) * p->l;
+        const double cost_pair = plan_work_split(tiles256, k_tiles, c->num_sms / 2).cost + 9.0;
+        const double cost_single = plan_work_split(tiles128, k_tiles, c->num_sms).cost * 0.9 + 4.5;
+        if (cost_single < cost_pair) cg = 1;
+    }
     int bn = cf.tile_n;
     if (bn == 0) {
         bn = (p->n % 256 == 0) ? 256 : 128;
         // single-CTA tiles that would leave SMs idle: halve the tile width to double the tile count
         const long long tiles256 = static_cast<long long>((p->m + kBM - 1) / kBM) * (p->n / 256) * p->l;
-        if (cg == 1 && bn == 256 && tiles256 < c->num_sms) bn = 128;
+        if (cg == 1 && bn == 256 && (tiles256 < c->num_sms || (cf.cta_group == 0 && p->m > kBM))) bn = 128;
     }
     if (p->n % bn) return fail(NVFP4_ERR_INVALID_ARGUMENT, "n = %d is not a multiple of tile_n = %d", p->n, bn);
 
