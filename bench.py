@@ -211,6 +211,7 @@ def main():
                          "auto = fused on 2 GPUs, push on more (the measured best of each)")
     ap.add_argument("--panels", type=int, default=0, help="N > 1: row panels the exchange is pipelined over (all modes but fused); 0 = the measured best")
     ap.add_argument("--copy-sms", type=int, default=-1, help="N > 1, push / pull: SMs reserved for the copy kernel (the GEMM runs on the rest); -1 = the measured best")
+    ap.add_argument("--peer-tma", type=int, default=-1, help="N > 1, fused: peers served by tensor stores instead of the epilogue warps' own stores; -1 = the library default")
     ap.add_argument("--nvfp4-out", action="store_true", help="N = 1, GEMM workloads: time the re-quantising epilogue variant (NVFP4 output) instead")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary per-config table")
@@ -592,6 +593,9 @@ def bench_column_parallel(args, w, rank, world, dev):
 
     m, n, k = w["m"], w["n"], w["k"]
     shard = plan_shard(n, world, rank)
+    if args.peer_tma >= 0:
+        from nvfp4_gemm_b200 import _lib
+        _lib.load().nvfp4_set_peer_tma_limit(args.peer_tma)
     # every rank builds the same full B from the seed and keeps its rows (inputs are synthetic)
     n_sets = 2
     sets, host_sets = [], []

@@ -155,6 +155,14 @@ int nvfp4_gemm_allgather(const nvfp4_problem* problem, const nvfp4_gemm_config* 
                          void* stream);
 
 /*
+ * How nvfp4_gemm_allgather reaches the peers: with at most `peers` of them, every staged block of
+ * the output goes to each peer by one more tensor store (TMA) beside the local one; with more, the
+ * epilogue warps store the block themselves (many destinations' tensor maps in play made the
+ * tensor stores slow).  Clamped to 0..7; returns the previous value (default 1).
+ */
+int nvfp4_set_peer_tma_limit(int peers);
+
+/*
  * All-gather by a copy kernel: copies rows [row0, row0 + rows) of n_blocks (<= 7) column blocks,
  * each n_local fp16 wide inside a row-major matrix of row_stride elements, from src_blocks[i] to
  * dst_blocks[i].  Either side may be another GPU's peer-mapped output (already offset to the

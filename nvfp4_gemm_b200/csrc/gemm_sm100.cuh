@@ -67,6 +67,11 @@ struct GemmParams {
     // stores only; nothing is ever loaded from a peer).
     __half* c_peer[7];
     int n_peer;
+    // With few peers the TMA-store epilogue sends each peer its copy of a staged block with one more
+    // tensor store (tma_c_peer[i] describes c_peer[i] like tma_c describes c); with many, the
+    // epilogue warps store the block themselves.
+    int peer_tma;
+    CUtensorMap tma_c_peer[7];
     // Extended epilogue (kernels instantiated with EPI_EX): out = act(acc + bias[column]), written
     // as fp16 to c, or re-quantised to NVFP4 (packed e2m1 + one e4m3 scale per 16 columns of a row,
     // the operand format of a following GEMM whose K is this GEMM's N).
@@ -295,6 +300,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
         ptx::prefetch_tensormap(&p.tma_sfa);
         ptx::prefetch_tensormap(&p.tma_sfb);
         if (TMA_STORE) ptx::prefetch_tensormap(&p.tma_c);
+        if (TMA_STORE && p.peer_tma)
+            for (int r = 0; r < p.n_peer; ++r) ptx::prefetch_tensormap(&p.tma_c_peer[r]);
     }
     __syncthreads();  // barriers initialised
     bool cluster_waited = true;
@@ -845,13 +852,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(const __gri
                         __syncwarp();
                         if (lane == 0 && mb * kBM + quad * 32 < p.M) {  // rows past M inside the box are clipped; one fixed lane owns the bulk groups
                             ptx::tma_store_3d(&p.tma_c, staging + store_buf * 4096, nb * BN + chunk_at(2 * ci) * 32, mb * kBM + quad * 32, l);
+                            if (p.peer_tma)   // the same block to every peer, in the same bulk group: the buffer is free when all have read it
+                                for (int r = 0; r < p.n_peer; ++r)
+                                    ptx::tma_store_3d(&p.tma_c_peer[r], staging + store_buf * 4096, nb * BN + chunk_at(2 * ci) * 32, mb * kBM + quad * 32, l);
                             ptx::bulk_commit_group();
                         }
-                        if (p.n_peer > 0) {
+                        if (p.n_peer > 0 && !p.peer_tma) {
                             // Peers get the same 32 x 128-byte block with plain vector stores read back
                             // from the staging buffer: a warp instruction covers four full 128-byte
-                            // rows.  (One TMA store per peer was tried first: with a tensor map per
-                            // destination the stores crawled once there were more than a few maps.)
+                            // rows.  (With a tensor store per peer instead, the stores crawled once
+                            // there were more than a few destinations' tensor maps in play.)
                             const int sub = lane >> 3, piece = lane & 7;
                             uint4 q[8];
 #pragma unroll

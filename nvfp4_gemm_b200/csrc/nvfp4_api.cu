@@ -401,6 +401,11 @@ int validate_gemm(const nvfp4_problem* p, bool needs_c = true) {
 }  // namespace
 
 namespace {
+// Up to this many peers get their copies of the output by tensor stores (one per peer and staged
+// block); more are served by the epilogue warps' own stores.
+std::atomic<int> g_peer_tma_limit{1};
+int peer_tma_limit() { return g_peer_tma_limit.load(); }
+
 int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, const nvfp4_epilogue* epi, void* const* c_peers, int n_peers,
               void* stream_v) {
     const bool to_nvfp4 = epi && epi->output == NVFP4_OUT_NVFP4;
@@ -544,6 +549,13 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, const nvfp4_
         if (int rc = get_map(c, make_key(p->c, p->n, p->m, p->l, static_cast<uint64_t>(p->c_row_stride) * 2, c_bs, 64, 32,
                                          CU_TENSOR_MAP_DATA_TYPE_FLOAT16),
                              &g.tma_c)) return rc;
+        if (n_peers > 0 && n_peers <= peer_tma_limit()) {
+            g.peer_tma = 1;
+            for (int i = 0; i < n_peers; ++i)
+                if (int rc = get_map(c, make_key(c_peers[i], p->n, p->m, p->l, static_cast<uint64_t>(p->c_row_stride) * 2, c_bs, 64, 32,
+                                                 CU_TENSOR_MAP_DATA_TYPE_FLOAT16),
+                                     &g.tma_c_peer[i])) return rc;
+        }
     }
 
     // Decode shapes (one 128-row block, fewer tiles than half the SMs): split K across a cluster
@@ -1001,6 +1013,12 @@ int nvfp4_plan_tile(int total_units, int workers, int k_tiles, int tiles_m, int 
     return NVFP4_OK;
 }
 
+
+int nvfp4_set_peer_tma_limit(int peers) {
+    if (peers < 0) peers = 0;
+    if (peers > 7) peers = 7;
+    return g_peer_tma_limit.exchange(peers);
+}
 
 uint64_t nvfp4_launch_count(void) { return g_launches.load(); }
 

@@ -21,9 +21,10 @@ def cuda_lib(lib):
     return lib
 
 
+@pytest.mark.parametrize("tma_peers", [0, 7])      # peers served by the epilogue warps' stores / by tensor stores
 @pytest.mark.parametrize("m,n_local,k,blocks,rank,n_peers", [(512, 512, 1024, 2, 1, 1), (300, 256, 2048, 4, 2, 3), (128, 256, 4096, 2, 0, 1),
                                                             (1024, 1024, 512, 8, 5, 7)])
-def test_gemm_stores_its_column_block_into_every_peer_buffer(cuda_lib, oracle, m, n_local, k, blocks, rank, n_peers):
+def test_gemm_stores_its_column_block_into_every_peer_buffer(cuda_lib, oracle, m, n_local, k, blocks, rank, n_peers, tma_peers):
     from nvfp4_gemm_b200 import _lib
     from nvfp4_gemm_b200.inputs import generate_input
     from nvfp4_gemm_b200.submission import make_problem
@@ -34,8 +35,12 @@ def test_gemm_stores_its_column_block_into_every_peer_buffer(cuda_lib, oracle, m
     begin = rank * n_local
     problem = make_problem(tuple(data[:6]) + (outs[0][:, begin:begin + n_local],))
     peers = (ctypes.c_void_p * n_peers)(*[o.data_ptr() + begin * 2 for o in outs[1:]])
-    _lib.check(cuda_lib.nvfp4_gemm_allgather(problem, None, peers, n_peers, torch.cuda.current_stream().cuda_stream))
-    _lib.check(cuda_lib.nvfp4_check_status(torch.cuda.current_stream().cuda_stream))
+    previous = cuda_lib.nvfp4_set_peer_tma_limit(tma_peers)
+    try:
+        _lib.check(cuda_lib.nvfp4_gemm_allgather(problem, None, peers, n_peers, torch.cuda.current_stream().cuda_stream))
+        _lib.check(cuda_lib.nvfp4_check_status(torch.cuda.current_stream().cuda_stream))
+    finally:
+        cuda_lib.nvfp4_set_peer_tma_limit(previous)
     a, b, sfa, sfb = oracle.tensors_to_numpy(data)
     exp = oracle.ref_gemm_c(a, b, sfa, sfb)
     for i, o in enumerate(outs):
