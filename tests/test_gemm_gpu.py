@@ -14,6 +14,10 @@ TASK_SHAPES = [
 ]
 # ... plus ragged M, batched L, N that only fits the 128-wide tile, and a single k-tile
 EXTRA_SHAPES = [(1, 128, 256, 1), (130, 384, 512, 1), (300, 768, 1536, 2), (128, 128, 256, 3), (257, 640, 1024, 2)]
+# ... and mid-size shapes on either side of the launch code's choices: whole tiles on fewer CTA pairs
+# than the device has, two waves of whole tiles, 128-wide single-CTA tiles for an odd number of
+# 128-row blocks
+MID_SHAPES = [(768, 4096, 4096, 1), (1024, 7168, 4096, 1), (640, 7168, 7168, 1), (1536, 4096, 4096, 1)]
 
 
 @pytest.fixture(scope="module")
@@ -24,7 +28,7 @@ def sub(lib):
     return submission
 
 
-@pytest.mark.parametrize("shape", TASK_SHAPES + EXTRA_SHAPES)
+@pytest.mark.parametrize("shape", TASK_SHAPES + EXTRA_SHAPES + MID_SHAPES)
 def test_custom_kernel_matches_oracle_bit_exact(sub, oracle, shape):
     from nvfp4_gemm_b200.inputs import generate_input
     m, n, k, l = shape
