@@ -1,11 +1,13 @@
 // NVFP4 block-scaled GEMM for sm_100a:  C[M,N] (fp16) = (A x SFA) . (B x SFB)^T.
 //
 // Persistent workers walk a contiguous range of (output tile, k-tile) work units ("stream-K"):
-// every worker gets the same number of units, so small-M decode shapes fill all SMs and large
-// shapes have no partial last wave.  A tile whose k-range one worker covers is written straight
-// to C.  A tile shared by several workers is published as fp32 partials in per-worker scratch
-// slots; whichever worker completes the tile's k-tile count sums the partials in a fixed order
-// (deterministic) and writes fp16.
+// every worker gets the same number of units, so large shapes have no partial last wave; or, when
+// the launch code finds that cheaper, whole tiles only (GemmParams::whole_tiles).  A tile whose
+// k-range one worker covers is written straight to C.  A tile shared by several workers is
+// published as fp32 partials in per-worker scratch slots by all but the worker that holds the
+// start of its k-range, which sums the partials in a fixed order (deterministic) and writes fp16;
+// SegmentPlan orders a worker's pieces so that this summing runs beside later whole tiles.
+// Decode shapes (one 128-row block) split K over a cluster instead (KS > 1).
 //
 // A worker is one CTA (CG = 1: 128 x BN tile) or a CTA pair running tcgen05 with cta_group::2
 // (CG = 2: 256 x BN tile; each CTA holds 128 rows of A, BN/2 rows of B and its own 128
@@ -14,10 +16,11 @@
 // Warp roles (192 threads per CTA):
 //   warp 0      TMA producer: A/B tiles (128-byte swizzle) and the 512-byte scale atoms of the
 //               permuted layout into a STAGES-deep shared-memory ring (full/empty mbarriers)
-//   warp 1      TMEM owner.  Leader CTA: MMA issuer -- tcgen05.cp scale atoms -> TMEM, four
-//               tcgen05.mma.kind::mxf4nvf4.block_scale (K = 64 each) per stage, tcgen05.commit
-//               to release the stage / publish the accumulator.  In a pair both CTAs' loads
-//               signal the leader's full barrier (cp.async.bulk.tensor .cta_group::2).
+//   warp 1      TMEM owner.  Leader CTA: MMA issuer, ONE thread elected once -- tcgen05.cp scale
+//               atoms -> TMEM, four tcgen05.mma.kind::mxf4nvf4.block_scale (K = 64 each) per
+//               stage, tcgen05.commit to release the stage / publish the accumulator.  In a pair
+//               both CTAs' loads signal the leader's full barrier (cp.async.bulk.tensor
+//               .cta_group::2).
 //   warps 2..5  epilogue: tcgen05.ld -> fp16 -> TMA store (or 16-byte stores), or the fp32
 //               partial-tile path
 //
