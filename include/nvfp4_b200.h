@@ -315,6 +315,18 @@ int nvfp4_selftest_bounded_wait(void* stream);
 int nvfp4_plan_units(int total_units, int grid, int cta, int* begin, int* end, int* first_tile_slot, int k_tiles);
 
 /*
+ * Host-side view of how a launch shares `tiles` output tiles of `k_tiles` k-tiles each among at
+ * most `max_workers` persistent workers (CTAs, or CTA pairs) when the caller leaves the grid to
+ * the library: *whole_tiles = 1 and *workers = the fewest workers that need no more waves (the work
+ * is split at tile boundaries only), or *whole_tiles = 0 and *workers = max_workers (an even split
+ * of all (tile, k-tile) units; tiles shared between workers are summed through scratch).  The choice
+ * is the smaller of two estimates in k-tiles of run time: waves x k_tiles, and units / workers plus
+ * 3 (a worker has two tiles' worth of units or more: the summing hides behind whole tiles) or 12 per
+ * worker that shares a tile (at least 24).
+ */
+int nvfp4_plan_work_split(int64_t tiles, int k_tiles, int max_workers, int* workers, int* whole_tiles);
+
+/*
  * The order in which a persistent worker walks its range: segment `index` (0, 1, ...) as a
  * half-open unit range inside ONE output tile, or begin = end = -1 past the last one.  Order: the
  * partial tile the range starts in, the whole tiles but the last, the partial tile the range ends

@@ -241,8 +241,9 @@ bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) %
 // through scratch?  In k-tiles of run time: whole tiles cost waves x k_tiles; the even split costs
 // units / workers plus the summing, which hides behind later whole tiles when a worker has at
 // least two tiles' worth of units and otherwise ends the launch (publish, wait, read back:
-// measured about as long as 24 k-tiles of the 256-wide pair kernel -- 768 x 4096 x 4096 took
-// 19.5 us split 74 ways and 10.6 us as 48 whole tiles).
+// measured about as long as 24 k-tiles of the 256-wide pair kernel with two workers per tile --
+// 768 x 4096 x 4096 took 19.5 us split 74 ways and 10.6 us as 48 whole tiles -- and counted as 12
+// k-tiles per worker that shares a tile).
 struct WorkSplit {
     double cost;        // k-tiles of run time
     int workers;
@@ -253,7 +254,8 @@ WorkSplit plan_work_split(long long tiles, int k_tiles, int max_workers) {
     const long long waves = (tiles + whole_workers_max - 1) / whole_workers_max;
     const double cost_whole = static_cast<double>(waves) * k_tiles;
     const double share = static_cast<double>(tiles) * k_tiles / max_workers;
-    const double cost_split = share + (share >= 2.0 * k_tiles ? 3.0 : 24.0);
+    const double per_tile = static_cast<double>(k_tiles) / (share < 1.0 ? 1.0 : share);   // workers that share a tile, about
+    const double cost_split = share + (share >= 2.0 * k_tiles ? 3.0 : 12.0 * (per_tile < 2.0 ? 2.0 : per_tile));
     if (cost_whole <= cost_split) return WorkSplit{cost_whole, static_cast<int>((tiles + waves - 1) / waves), true};   // the fewest workers that need no more waves
     return WorkSplit{cost_split, max_workers, false};
 }
@@ -998,6 +1000,14 @@ int nvfp4_plan_segment(int total_units, int grid, int cta, int k_tiles, int inde
     }
     *begin = seg.u0;
     *end = seg.u1;
+    return NVFP4_OK;
+}
+
+int nvfp4_plan_work_split(int64_t tiles, int k_tiles, int max_workers, int* workers, int* whole_tiles) {
+    if (tiles < 1 || k_tiles < 1 || max_workers < 1 || !workers || !whole_tiles) return fail(NVFP4_ERR_INVALID_ARGUMENT, "bad work-split query");
+    const WorkSplit split = plan_work_split(tiles, k_tiles, max_workers);
+    *workers = split.workers;
+    *whole_tiles = split.whole_tiles ? 1 : 0;
     return NVFP4_OK;
 }
 

@@ -141,6 +141,25 @@ def test_segment_order_partitions_a_workers_range_and_ends_on_a_whole_tile(lib, 
     assert lib.nvfp4_plan_segment(total, grid, grid, kt, 0, ctypes.byref(sb), ctypes.byref(se)) == _lib.NVFP4_ERR_INVALID_ARGUMENT
 
 
+@pytest.mark.parametrize("tiles,k_tiles,max_workers,exp_workers,exp_whole", [
+    (448, 28, 74, 74, 0),        # 4096 x 7168 x 7168 on pairs: 6.05 tiles per worker, even split
+    (3584, 32, 74, 74, 0),       # 8192 x 28672 x 8192
+    (162, 28, 74, 74, 0),        # 2304 x 4608 x 7168: 2.2 tiles per worker, the summing hides behind whole tiles
+    (48, 16, 74, 48, 1),         # 768 x 4096 x 4096: fewer tiles than pairs, one whole tile each
+    (112, 16, 74, 56, 1),        # 1024 x 7168 x 4096: two waves, on the fewest workers that need two
+    (56, 8, 148, 56, 1),         # 128 x 7168 x 2048 on single CTAs
+    (1, 64, 148, 1, 1),
+])
+def test_work_split_choice(lib, tiles, k_tiles, max_workers, exp_workers, exp_whole):
+    w, whole = ctypes.c_int(), ctypes.c_int()
+    assert lib.nvfp4_plan_work_split(tiles, k_tiles, max_workers, ctypes.byref(w), ctypes.byref(whole)) == 0
+    assert (w.value, whole.value) == (exp_workers, exp_whole)
+    if whole.value:                                        # no more waves than the full device would need
+        waves = -(-tiles // min(tiles, max_workers))
+        assert -(-tiles // w.value) == waves
+    assert lib.nvfp4_plan_work_split(0, k_tiles, max_workers, ctypes.byref(w), ctypes.byref(whole)) == _lib.NVFP4_ERR_INVALID_ARGUMENT
+
+
 def test_bench_roofline_arithmetic_matches_the_stated_work():
     """Algorithmic flops / bytes per launch that bench.py divides by the measured time: the
     figures of the task's configurations (2*M*N*K*L and the packed operand, scale and output bytes)."""
