@@ -327,6 +327,15 @@ int nvfp4_plan_units(int total_units, int grid, int cta, int* begin, int* end, i
 int nvfp4_plan_work_split(int64_t tiles, int k_tiles, int max_workers, int* workers, int* whole_tiles);
 
 /*
+ * Host-side view of the tile a GEMM of this shape gets on a device with num_sms SMs when the
+ * caller fixes nothing (cluster split-K aside, which decode shapes take first): *cta_group = 2 for
+ * 256-row tiles on CTA pairs or 1, *tile_n = 128 or 256.  Pairs with 256 x 256 tiles unless the
+ * estimate above, with a 128-wide stage counted as 0.9 of the pair's and the last epilogue as 4.5
+ * against 9 k-tiles, says that 128 x 128 tiles on single CTAs finish sooner.
+ */
+int nvfp4_plan_tile_shape(int m, int n, int k, int l, int num_sms, int* cta_group, int* tile_n);
+
+/*
  * The order in which a persistent worker walks its range: segment `index` (0, 1, ...) as a
  * half-open unit range inside ONE output tile, or begin = end = -1 past the last one.  Order: the
  * partial tile the range starts in, the whole tiles but the last, the partial tile the range ends

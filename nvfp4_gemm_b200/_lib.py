@@ -22,7 +22,7 @@ EXPORTED_SYMBOLS = (
     "nvfp4_shutdown", "nvfp4_last_error", "nvfp4_version", "nvfp4_plan_units", "nvfp4_gemm_static_scratch",
     "nvfp4_interleave_column_blocks", "nvfp4_permute_scales", "nvfp4_gemm_allgather", "nvfp4_quantize", "nvfp4_copy_2d", "nvfp4_copy_column_blocks",
     "nvfp4_unpermute_scales", "nvfp4_compare_scale_layouts", "nvfp4_gemv_config", "nvfp4_release_stream",
-    "nvfp4_gemm_epilogue", "nvfp4_plan_tile", "nvfp4_plan_segment", "nvfp4_plan_work_split", "nvfp4_set_peer_tma_limit", "nvfp4_comm_export", "nvfp4_comm_open", "nvfp4_comm_close",
+    "nvfp4_gemm_epilogue", "nvfp4_plan_tile", "nvfp4_plan_segment", "nvfp4_plan_work_split", "nvfp4_plan_tile_shape", "nvfp4_set_peer_tma_limit", "nvfp4_comm_export", "nvfp4_comm_open", "nvfp4_comm_close",
 )
 COMM_HANDLE_BYTES = 64
 
@@ -132,6 +132,8 @@ def load() -> ctypes.CDLL:
     lib.nvfp4_plan_tile.restype = c_int
     lib.nvfp4_plan_work_split.argtypes = [ctypes.c_int64, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int)]
     lib.nvfp4_plan_work_split.restype = c_int
+    lib.nvfp4_plan_tile_shape.argtypes = [c_int] * 5 + [ctypes.POINTER(c_int)] * 2
+    lib.nvfp4_plan_tile_shape.restype = c_int
     lib.nvfp4_set_peer_tma_limit.argtypes = [c_int]
     lib.nvfp4_set_peer_tma_limit.restype = c_int
     lib.nvfp4_plan_segment.argtypes = [c_int] * 5 + [ctypes.POINTER(c_int)] * 2

@@ -408,6 +408,38 @@ namespace {
 std::atomic<int> g_peer_tma_limit{1};
 int peer_tma_limit() { return g_peer_tma_limit.load(); }
 
+// Tile shape of the persistent kernels: what the caller fixed in cf, else this library's choice.
+struct TileChoice {
+    int cta_group, tile_n;
+};
+TileChoice choose_tile(int m, int n, int k, int l, int num_sms, const nvfp4_gemm_config& cf) {
+    // A CTA pair (256-row tile, B shared through the pair) pays off as soon as there is more than
+    // one 128-row block; decode shapes (m <= 128) stay on single CTAs.
+    int cg = cf.cta_group;
+    if (cg == 0) cg = (m > kBM && n % 256 == 0) ? 2 : 1;
+    if (cf.cta_group == 0 && cf.tile_n == 0 && cg == 2 && cf.grid == 0 && cf.split_k <= 1) {
+        // 256 x 256 tiles on CTA pairs do twice the work per SM and stage of 128 x 128 tiles on
+        // single CTAs, but small problems fill more SMs with the small tiles and their epilogue is
+        // shorter.  Estimated run time in k-tiles of the pair kernel (one of its stages ~ 0.35 us;
+        // a 128-wide stage 0.9 of that, the epilogues of the last tile 9 and 4.5), constants fitted
+        // to thirteen measured shapes from 256 x 7168 x 256 to 4096 x 7168 x 7168.
+        const int k_tiles = k / kKPerStage;
+        const long long tiles256 = static_cast<long long>((m + 2 * kBM - 1) / (2 * kBM)) * (n / 256) * l;
+        const long long tiles128 = static_cast<long long>((m + kBM - 1) / kBM) * (n / 128) * l;
+        const double cost_pair = plan_work_split(tiles256, k_tiles, num_sms / 2).cost + 9.0;
+        const double cost_single = plan_work_split(tiles128, k_tiles, num_sms).cost * 0.9 + 4.5;
+        if (cost_single < cost_pair) cg = 1;
+    }
+    int bn = cf.tile_n;
+    if (bn == 0) {
+        bn = (n % 256 == 0) ? 256 : 128;
+        // single-CTA tiles that would leave SMs idle: halve the tile width to double the tile count
+        const long long tiles256 = static_cast<long long>((m + kBM - 1) / kBM) * (n / 256) * l;
+        if (cg == 1 && bn == 256 && (tiles256 < num_sms || (cf.cta_group == 0 && m > kBM))) bn = 128;
+    }
+    return TileChoice{cg, bn};
+}
+
 int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, const nvfp4_epilogue* epi, void* const* c_peers, int n_peers,
               void* stream_v) {
     const bool to_nvfp4 = epi && epi->output == NVFP4_OUT_NVFP4;
@@ -455,30 +487,9 @@ int gemm_impl(const nvfp4_problem* p, const nvfp4_gemm_config* cfg, const nvfp4_
     if (int rc = ensure_scratch(c)) return rc;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
-    // A CTA pair (256-row tile, B shared through the pair) pays off as soon as there is more than
-    // one 128-row block; decode shapes (m <= 128) stay on single CTAs.
-    int cg = cf.cta_group;
-    if (cg == 0) cg = (p->m > kBM && p->n % 256 == 0) ? 2 : 1;
-    if (cf.cta_group == 0 && cf.tile_n == 0 && cg == 2 && cf.grid == 0 && cf.split_k <= 1) {
-        // 256 x 256 tiles on CTA pairs do twice the work per SM and stage of 128 x 128 tiles on
-        // single CTAs, but small problems fill more SMs with the small tiles and their epilogue is
-        // shorter.  Estimated run time in k-tiles of the pair kernel (one of its stages ~ 0.35 us;
-        // a 128-wide stage 0.9 of that, the epilogues of the last tile 9 and 4.5), constants fitted
-        // to thirteen measured shapes from 256 x 7168 x 256 to 4096 x 7168 x 7168.
-        const int k_tiles = p->k / kKPerStage;
-        const long long tiles256 = static_cast<long long>((p->m + 2 * kBM - 1) / (2 * kBM)) * (p->n / 256) * p->l;
-        const long long tiles128 = static_cast<long long>((p->m + kBM - 1) / kBM) * (p->n / 128) * p->l;
-        const double cost_pair = plan_work_split(tiles256, k_tiles, c->num_sms / 2).cost + 9.0;
-        const double cost_single = plan_work_split(tiles128, k_tiles, c->num_sms).cost * 0.9 + 4.5;
-        if (cost_single < cost_pair) cg = 1;
-    }
-    int bn = cf.tile_n;
-    if (bn == 0) {
-        bn = (p->n % 256 == 0) ? 256 : 128;
-        // single-CTA tiles that would leave SMs idle: halve the tile width to double the tile count
-        const long long tiles256 = static_cast<long long>((p->m + kBM - 1) / kBM) * (p->n / 256) * p->l;
-        if (cg == 1 && bn == 256 && (tiles256 < c->num_sms || (cf.cta_group == 0 && p->m > kBM))) bn = 128;
-    }
+    const TileChoice choice = choose_tile(p->m, p->n, p->k, p->l, c->num_sms, cf);
+    const int cg = choice.cta_group;
+    int bn = choice.tile_n;
     if (p->n % bn) return fail(NVFP4_ERR_INVALID_ARGUMENT, "n = %d is not a multiple of tile_n = %d", p->n, bn);
 
     GemmParams g;
@@ -1000,6 +1011,16 @@ int nvfp4_plan_segment(int total_units, int grid, int cta, int k_tiles, int inde
     }
     *begin = seg.u0;
     *end = seg.u1;
+    return NVFP4_OK;
+}
+
+int nvfp4_plan_tile_shape(int m, int n, int k, int l, int num_sms, int* cta_group, int* tile_n) {
+    if (m < 1 || n < 128 || n % 128 || k < kKPerStage || k % kKPerStage || l < 1 || num_sms < 2 || !cta_group || !tile_n)
+        return fail(NVFP4_ERR_INVALID_ARGUMENT, "bad tile-shape query");
+    const nvfp4_gemm_config cf = {0, 0, 0, 0, 0, 0};
+    const TileChoice choice = choose_tile(m, n, k, l, num_sms, cf);
+    *cta_group = choice.cta_group;
+    *tile_n = choice.tile_n;
     return NVFP4_OK;
 }
 

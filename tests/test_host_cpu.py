@@ -160,6 +160,22 @@ def test_work_split_choice(lib, tiles, k_tiles, max_workers, exp_workers, exp_wh
     assert lib.nvfp4_plan_work_split(0, k_tiles, max_workers, ctypes.byref(w), ctypes.byref(whole)) == _lib.NVFP4_ERR_INVALID_ARGUMENT
 
 
+@pytest.mark.parametrize("m,n,k,exp", [
+    (4096, 7168, 7168, (2, 256)), (8192, 28672, 8192, (2, 256)), (2304, 4608, 7168, (2, 256)),      # large: pairs
+    (512, 7168, 2048, (2, 256)), (768, 4096, 4096, (2, 256)), (1024, 7168, 4096, (2, 256)), (384, 7168, 2304, (2, 256)),
+    (1536, 4096, 4096, (2, 256)),
+    (1024, 4096, 1024, (1, 128)), (640, 7168, 7168, (1, 128)), (512, 1536, 7168, (1, 128)), (256, 7168, 256, (1, 128)),
+    (512, 4096, 512, (1, 128)), (256, 7168, 2048, (1, 128)),                                          # small / short K: single CTAs
+    (128, 7168, 2048, (1, 128)), (256, 384, 1024, (1, 128)),                                          # one row block; N not a multiple of 256
+])
+def test_tile_shape_choice_on_a_148_sm_device(lib, m, n, k, exp):
+    """The choices measured on a B200 (each row was timed with both tiles; the faster one is expected)."""
+    cg, bn = ctypes.c_int(), ctypes.c_int()
+    assert lib.nvfp4_plan_tile_shape(m, n, k, 1, 148, ctypes.byref(cg), ctypes.byref(bn)) == 0
+    assert (cg.value, bn.value) == exp
+    assert lib.nvfp4_plan_tile_shape(m, n + 1, k, 1, 148, ctypes.byref(cg), ctypes.byref(bn)) == _lib.NVFP4_ERR_INVALID_ARGUMENT
+
+
 def test_bench_roofline_arithmetic_matches_the_stated_work():
     """Algorithmic flops / bytes per launch that bench.py divides by the measured time: the
     figures of the task's configurations (2*M*N*K*L and the packed operand, scale and output bytes)."""
